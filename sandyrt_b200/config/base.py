@@ -38,10 +38,12 @@ class ModelConfig:
 
 
 def architecture_name(raw: Dict[str, Any]) -> str:
-    """The registry key of a parsed config.json: `architectures[0]`."""
+    """The registry key of a parsed config.json: `architectures[0]`, or the one name under `architecture`."""
     archs = raw.get("architectures")
+    if archs is None and isinstance(raw.get("architecture"), str):
+        return raw["architecture"]
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
+        raise ConfigError("config.json: 'architectures' must be a non-empty list of names (or 'architecture' one name)")
     return archs[0]
 
 

@@ -163,6 +163,11 @@ std::vector<CacheSpec> cache_specs_from(const Json& j) {
             std::vector<int64_t> shape;
             for (const Json& d : s.at("shape").items()) shape.push_back(d.as_int());
             out.push_back(CacheSpec::state(shape));
+        } else if (kind == "paged_state") {
+            std::vector<int64_t> shape;
+            for (const Json& d : s.at("shape").items()) shape.push_back(d.as_int());
+            out.push_back(CacheSpec::paged_with_state((int)s.at("n_kv_heads").as_int(), (int)s.at("head_dim").as_int(),
+                                                      (int)geti(s, "window", 0), shape));
         } else throw CacheError("unknown cache spec kind '" + kind + "'");
     }
     return out;

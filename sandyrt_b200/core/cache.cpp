@@ -26,6 +26,14 @@ CacheSpec CacheSpec::state(std::vector<int64_t> shape, DType dtype) {
     s.state_dtype = dtype;
     return s;
 }
+CacheSpec CacheSpec::paged_with_state(int n_kv_heads, int head_dim, int window, std::vector<int64_t> shape, DType dtype) {
+    CacheSpec s = paged(n_kv_heads, head_dim, window);
+    s.kind = Kind::PagedState;
+    s.state_shape = std::move(shape);
+    s.state_dtype = dtype;
+    return s;
+}
+CacheSpec CacheSpec::pages_only() const { return has_pages() ? paged(n_kv_heads, head_dim, window) : none(); }
 bool CacheSpec::operator==(const CacheSpec& o) const {
     return kind == o.kind && n_kv_heads == o.n_kv_heads && head_dim == o.head_dim && window == o.window &&
            state_shape == o.state_shape && state_dtype == o.state_dtype;
@@ -76,11 +84,12 @@ CacheLayout CacheLayout::from_specs(const std::vector<CacheSpec>& specs, int pag
     out.page_size = page_size;
     for (size_t ci = 0; ci < specs.size(); ci++) {
         const CacheSpec& spec = specs[ci];
-        if (spec.kind == CacheSpec::Kind::None) continue;
-        if (spec.kind == CacheSpec::Kind::State) { out.state_of_cache[(int)ci] = spec; continue; }
+        if (spec.has_state()) out.state_of_cache[(int)ci] = spec;
+        if (!spec.has_pages()) continue;
+        const CacheSpec pages = spec.pages_only();
         bool placed = false;
         for (auto& g : out.groups)
-            if (g.spec == spec) {
+            if (g.spec == pages) {
                 out.group_of_cache[(int)ci] = {g.index, (int)g.caches.size()};
                 g.caches.push_back((int)ci);
                 placed = true;
@@ -89,7 +98,7 @@ CacheLayout CacheLayout::from_specs(const std::vector<CacheSpec>& specs, int pag
         if (!placed) {
             CacheGroup g;
             g.index = (int)out.groups.size();
-            g.spec = spec;
+            g.spec = pages;
             g.caches = {(int)ci};
             out.group_of_cache[(int)ci] = {g.index, 0};
             out.groups.push_back(std::move(g));

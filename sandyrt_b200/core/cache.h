@@ -42,7 +42,9 @@ const char* dtype_name(DType d);
 
 // What a mixer may ask of the cache manager.
 struct CacheSpec {
-    enum class Kind { None, PagedKV, State };
+    // PagedState: pages and a fixed-size state together (a mixer that runs softmax attention beside a
+    // recurrence); the page fields and the state fields below are both in use then.
+    enum class Kind { None, PagedKV, State, PagedState };
     Kind kind = Kind::None;
     // PagedKV: keys and values of every position (or of the last `window` positions) in pages
     int n_kv_heads = 0, head_dim = 0;
@@ -55,6 +57,10 @@ struct CacheSpec {
     static CacheSpec none() { return CacheSpec(); }
     static CacheSpec paged(int n_kv_heads, int head_dim, int window = 0);
     static CacheSpec state(std::vector<int64_t> shape, DType dtype = DType::F32);
+    static CacheSpec paged_with_state(int n_kv_heads, int head_dim, int window, std::vector<int64_t> shape, DType dtype = DType::F32);
+    bool has_pages() const { return kind == Kind::PagedKV || kind == Kind::PagedState; }
+    bool has_state() const { return kind == Kind::State || kind == Kind::PagedState; }
+    CacheSpec pages_only() const;          // what decides the page group: the state fields dropped
     bool operator==(const CacheSpec& o) const;
     bool operator!=(const CacheSpec& o) const { return !(*this == o); }
 };

@@ -218,6 +218,15 @@ std::map<std::string, Architecture>& table() {
             return describe_gpt2(*g);
         };
         t[gpt2.name] = std::move(gpt2);
+        Architecture panupel;
+        panupel.name = PanupelConfig::kArchitecture;
+        panupel.parse = [](const Json& raw) { return std::unique_ptr<ModelConfig>(new PanupelConfig(PanupelConfig::from_json(raw))); };
+        panupel.describe = [](const ModelConfig& c) {
+            const auto* g = dynamic_cast<const PanupelConfig*>(&c);
+            if (!g) throw ConfigError("Panupel was given another architecture's configuration");
+            return describe_panupel(*g);
+        };
+        t[panupel.name] = std::move(panupel);
     });
     return t;
 }
@@ -269,8 +278,13 @@ Json read_config_json(const std::string& model_dir) {
 
 std::string architecture_name(const Json& raw) {
     const Json* a = raw.find("architectures");
+    if (!a) {
+        // some configurations name their one architecture under "architecture"
+        const Json* one = raw.find("architecture");
+        if (one && one->is_string()) return one->as_string();
+    }
     if (!a || !a->is_array() || a->size() == 0 || !a->items()[0].is_string())
-        throw ConfigError("config.json: 'architectures' must be a non-empty list of names");
+        throw ConfigError("config.json: 'architectures' must be a non-empty list of names (or 'architecture' one name)");
     return a->items()[0].as_string();
 }
 

@@ -54,6 +54,36 @@ public:
     void validate() const override;
 };
 
+// Panupel's config.json (core/panupel.cpp says what the keys mean).  Layers are listed one by one, each with its
+// own mixer type and sizes, so the typed form is a list of layer records.
+class PanupelConfig : public ModelConfig {
+public:
+    static constexpr const char* kArchitecture = "Panupel";
+    struct Layer {
+        std::string type;                                   // "parallel" | "delta"
+        int64_t heads = 0, kv_heads = 0, dim = 0, vdim = 0; // delta: the mixer's; parallel: the left mixer's
+        int64_t conv = 0;                                   // delta: taps of the short convolutions
+        double scale = 1.0;                                 // parallel, left: the factor on q . k
+        int64_t rot_dims = 0;                               // parallel, left: 0 = no rotary positions
+        double rot_base = 10000.0;
+        bool rot_scaling = false;
+        double rot_factor = 1.0, rot_low = 1.0, rot_high = 1.0, rot_original = 1.0;
+        int64_t right_heads = 0, right_dim = 0, right_vdim = 0;
+        double gate_cap = 1.0, left_scale = 1.0, right_scale = 1.0;
+        int64_t ff = 0;                                     // 0: the layer has no feed-forward
+    };
+    int64_t vocab = 0, width = 0;
+    double norm_eps = 1e-6, residual_mult = 1.0;
+    std::vector<Layer> layers;
+    bool has_loop = false;
+    int64_t loop_start = 0, loop_stop = 0, loop_times = 1;
+
+    static PanupelConfig from_json(const Json& raw);
+    std::string architecture() const override { return kArchitecture; }
+    Json to_json() const override;
+    void validate() const override;
+};
+
 // A configuration of an architecture defined outside this library: its normalised config.json
 // as the architecture's own `parse` returned it.
 class ForeignConfig : public ModelConfig {
@@ -80,12 +110,13 @@ const Architecture& get_architecture(const std::string& name);     // unknown ->
 std::vector<std::string> architectures();
 
 Json read_config_json(const std::string& model_dir);
-std::string architecture_name(const Json& raw);                    // architectures[0]
+std::string architecture_name(const Json& raw);                    // architectures[0], or the string under "architecture"
 std::unique_ptr<ModelConfig> parse_config(const Json& raw);         // chosen by the registry, validated
 std::unique_ptr<ModelConfig> load_config(const std::string& model_dir);
 std::string save_config(const ModelConfig& cfg, const std::string& model_dir);
 ModelSpec describe(const ModelConfig& cfg);
 
 ModelSpec describe_gpt2(const GPT2Config& cfg);
+ModelSpec describe_panupel(const PanupelConfig& cfg);
 
 }  // namespace sandy

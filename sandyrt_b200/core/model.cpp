@@ -16,14 +16,19 @@ Model::Model(ModelSpec spec) : spec_(std::move(spec)) {
             if (!p.norms.count(n)) missing += (missing.empty() ? "" : ", ") + n;
         if (!missing.empty()) throw ConfigError("block '" + l.block + "' needs norms " + missing);
         p.width = spec_.width;
+        p.params = l.block_params;
         if (!bf.make_block) throw ConfigError("part kind '" + l.block + "' is not a block");
         blocks_.push_back(bf.make_block(std::move(p)));
     }
     final_norm_ = make_part<Norm>("norm", spec_.final_norm);
     head_ = make_part<Head>("head", spec_.head);
-    for (const LayerCall& c : spec_.schedule)
+    for (const PartSpec& r : spec_.remixes) remixes_.push_back(make_part<Remix>("remix", r));
+    for (const LayerCall& c : spec_.schedule) {
         if (c.layer < 0 || c.layer >= (int)blocks_.size())
             throw ConfigError("run order names layer " + std::to_string(c.layer) + ", the model has " + std::to_string(blocks_.size()));
+        if (c.remix >= (int)remixes_.size())
+            throw ConfigError("run order names stream mix " + std::to_string(c.remix) + ", the model has " + std::to_string(remixes_.size()));
+    }
 }
 
 std::vector<Model::PartRef> Model::parts() const {
@@ -36,6 +41,7 @@ std::vector<Model::PartRef> Model::parts() const {
         out.push_back({&blocks_[i]->feed_forward(), &l.feed_forward});
         for (auto& kv : blocks_[i]->norms()) out.push_back({kv.second.get(), &l.norms.at(kv.first)});
     }
+    for (size_t i = 0; i < remixes_.size(); i++) out.push_back({remixes_[i].get(), &spec_.remixes[i]});
     out.push_back({final_norm_.get(), &spec_.final_norm});
     out.push_back({head_.get(), &spec_.head});
     return out;
@@ -97,6 +103,7 @@ size_t Model::weight_bytes() const {
         Block& b = *blocks_[(size_t)c.layer];
         total += b.mixer().weight_bytes() + b.feed_forward().weight_bytes();
         for (auto& kv : b.norms()) total += kv.second->weight_bytes();
+        if (c.remix >= 0) total += remixes_[(size_t)c.remix]->weight_bytes();
     }
     return total;
 }
@@ -106,7 +113,17 @@ Tensor Model::forward(StepContext& ctx) {
     ctx.position = position_.get();
     Tensor x = ws.get("stream", ctx.n_tokens, spec_.width, DType::F32);
     embedding_->forward(ctx, x);
-    for (const LayerCall& c : spec_.schedule) blocks_[(size_t)c.layer]->forward(ctx, x, c);
+    Tensor x0;
+    if (!remixes_.empty()) {
+        // the embedding's output stays at hand for the stream mixes
+        x0 = ws.get("stream_at_embedding", ctx.n_tokens, spec_.width, DType::F32);
+        cuda_check(cudaMemcpyAsync(x0.data, x.data, (size_t)x.numel() * sizeof(float), cudaMemcpyDeviceToDevice, ctx.launch.stream),
+                   "keeping the embedding's output");
+    }
+    for (const LayerCall& c : spec_.schedule) {
+        if (c.remix >= 0) remixes_[(size_t)c.remix]->forward(ctx, x, x0);
+        blocks_[(size_t)c.layer]->forward(ctx, x, c);
+    }
     Tensor logits = ws.get("logits", ctx.n_rows, spec_.vocab_size, DType::F32);
     if (ctx.n_rows) {
         Tensor y = ws.get("final_normed", ctx.n_rows, spec_.width, ctx.compute_dtype);

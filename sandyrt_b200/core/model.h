@@ -47,6 +47,7 @@ private:
     std::unique_ptr<Embedding> embedding_;
     std::unique_ptr<PositionEncoding> position_;
     std::vector<std::unique_ptr<Block>> blocks_;
+    std::vector<std::unique_ptr<Remix>> remixes_;
     std::unique_ptr<Norm> final_norm_;
     std::unique_ptr<Head> head_;
     bool bound_ = false;

@@ -477,8 +477,10 @@ bool decode_head_dim(DType dt, int d) {
 }  // namespace
 
 void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const KVView& c, Tensor& out, int n_heads,
-               float scale, int window, Workspace& ws) {
+               float scale, int window, Workspace& ws, const AttentionExtras* extras) {
     (void)ws;
+    const float* sk = extras ? extras->sink : nullptr;
+    const float* og = extras ? extras->out_gate : nullptr;
     const int d = c.head_dim, hkv = c.n_kv_heads;
     if (d % 16 != 0 || d > 256) throw UnsupportedShape("attention: head size " + std::to_string(d) + " must be a multiple of 16, at most 256");
     if (hkv <= 0 || n_heads % hkv != 0)
@@ -493,17 +495,17 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
     if (s.max_q_len > 1 && q.dtype == DType::BF16 && d <= 128) {
         static const bool use_tc = env_int("SANDYRT_PREFILL_TC", 1) != 0;     // 0 keeps every head size on the mma.sync kernel
         if (use_tc && d == 64) {
-            static auto fn = SANDY_KERNEL(attention_prefill_tc, sandy_prefill_attention_tc);
+            static auto fn = SANDY_KERNEL(attention_prefill_tc, sandy_prefill_attention_tc_ext);
             OpTimer timer(l, "attention, prompt (tcgen05)", attn_bytes, attn_flops);
             const int code = fn(q.data, (int)q.ld, c.k, c.v, c.page_stride, s.block_table, s.max_blocks, s.q_start, s.kv_before,
                                 out.data, (int)out.ld, s.n_seqs, s.max_q_len, n_heads, hkv, d, c.page_size, scale, window,
-                                c.num_pages, l.kernel_status, l.stream);
+                                c.num_pages, sk, og, l.kernel_status, l.stream);
             if (code != -1) { check(code, "prefill_attention_tc" + shape); return; }
         }
-        static auto fn = SANDY_KERNEL(attention_prefill, sandy_prefill_attention);
+        static auto fn = SANDY_KERNEL(attention_prefill, sandy_prefill_attention_ext);
         OpTimer timer(l, "attention, prompt (mma.sync)", attn_bytes, attn_flops);
         check(fn(q.data, (int)q.ld, c.k, c.v, c.page_stride, s.block_table, s.max_blocks, s.q_start, s.kv_before, out.data,
-                 (int)out.ld, s.n_seqs, s.max_q_len, n_heads, hkv, d, c.page_size, scale, window, c.num_pages, l.kernel_status,
+                 (int)out.ld, s.n_seqs, s.max_q_len, n_heads, hkv, d, c.page_size, scale, window, c.num_pages, sk, og, l.kernel_status,
                  l.stream),
               "prefill_attention" + shape);
         return;
@@ -524,44 +526,173 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
         if (mma_mode != 0 && q.dtype == DType::BF16 && d == 64 && !(bulk && splits == 1)) {
             static auto max_keys_fn = SANDY_KERNEL(attention_decode_mma, sandy_decode_attention_mma_max_keys);
             if (max_kv <= max_keys_fn(splits, c.page_size)) {
-                static auto fn = SANDY_KERNEL(attention_decode_mma, sandy_decode_attention_mma);
+                static auto fn = SANDY_KERNEL(attention_decode_mma, sandy_decode_attention_mma_ext);
                 OpTimer timer(l, "attention, decode (mma.sync)", attn_bytes, attn_flops);
                 check(fn(q.data, (int)q.ld, c.k, c.v, c.page_stride, s.block_table, s.max_blocks, s.token_seq, s.positions, out.data,
-                         (int)out.ld, T, n_heads, hkv, d, c.page_size, scale, window, splits, c.num_pages, max_kv, l.kernel_status,
+                         (int)out.ld, T, n_heads, hkv, d, c.page_size, scale, window, splits, c.num_pages, max_kv, sk, og, l.kernel_status,
                          l.stream),
                       "decode_attention_mma" + shape);
                 return;
             }
         }
         if (bulk) {
-            static auto fn = SANDY_KERNEL(attention_decode_bulk, sandy_decode_attention_bulk);
+            static auto fn = SANDY_KERNEL(attention_decode_bulk, sandy_decode_attention_bulk_ext);
             OpTimer timer(l, "attention, decode (bulk copies)", attn_bytes, attn_flops);
             check(fn(q.data, (int)q.ld, c.k, c.v, c.page_stride, s.block_table, s.max_blocks, s.token_seq, s.positions, out.data,
                      (int)out.ld, T, n_heads, hkv, d, c.page_size, scale, window, splits, c.num_pages, code_of(q.dtype),
-                     l.kernel_status, l.stream),
+                     sk, og, l.kernel_status, l.stream),
                   "decode_attention_bulk" + shape);
         } else if (splits > 1) {
-            static auto fn = SANDY_KERNEL(attention_decode, sandy_decode_attention_cluster);
+            static auto fn = SANDY_KERNEL(attention_decode, sandy_decode_attention_cluster_ext);
             OpTimer timer(l, "attention, decode (cluster)", attn_bytes, attn_flops);
             check(fn(q.data, (int)q.ld, c.k, c.v, c.page_stride, s.block_table, s.max_blocks, s.token_seq, s.positions, out.data,
                      (int)out.ld, T, n_heads, hkv, d, c.page_size, scale, window, splits, c.num_pages, code_of(q.dtype),
-                     l.kernel_status, l.stream),
+                     sk, og, l.kernel_status, l.stream),
                   "decode_attention_cluster" + shape);
         } else {
-            static auto fn = SANDY_KERNEL(attention_decode, sandy_decode_attention);
+            static auto fn = SANDY_KERNEL(attention_decode, sandy_decode_attention_ext);
             OpTimer timer(l, "attention, decode (one block)", attn_bytes, attn_flops);
             check(fn(q.data, (int)q.ld, c.k, c.v, c.page_stride, s.block_table, s.max_blocks, s.token_seq, s.positions, out.data,
                      (int)out.ld, nullptr, T, n_heads, hkv, d, c.page_size, scale, window, 1, c.num_pages, code_of(q.dtype),
-                     l.kernel_status, l.stream),
+                     sk, og, l.kernel_status, l.stream),
                   "decode_attention" + shape);
         }
         return;
     }
-    static auto fn = SANDY_KERNEL(attention, sandy_paged_attention);
+    static auto fn = SANDY_KERNEL(attention, sandy_paged_attention_ext);
     OpTimer timer(l, "attention, general", attn_bytes, attn_flops);
     check(fn(q.data, (int)q.ld, c.k, c.v, c.page_stride, s.block_table, s.max_blocks, s.token_seq, s.positions, out.data,
-             (int)out.ld, T, n_heads, hkv, d, c.page_size, scale, window, c.num_pages, code_of(q.dtype), l.kernel_status, l.stream),
+             (int)out.ld, T, n_heads, hkv, d, c.page_size, scale, window, c.num_pages, code_of(q.dtype), sk, og, l.kernel_status, l.stream),
           "paged_attention" + shape);
+}
+
+// ---- RMS norms, gates, casts ---------------------------------------------------------------------------
+void rmsnorm(const Launch& l, const Tensor& x, const Tensor* gain, float eps, Tensor& out, const int* rows, int n_rows) {
+    if (x.dtype != DType::F32 || (gain && (gain->dtype != DType::F32 || gain->numel() != x.cols)) || out.cols != x.cols ||
+        out.rows < n_rows || (!rows && x.rows < n_rows))
+        throw KernelError("rmsnorm: float32 x [rows, width], float32 gain [width], out [n_rows, width] expected");
+    if (left_out("layernorm")) return;
+    static auto fn = SANDY_KERNEL(rmsnorm, sandy_rmsnorm);
+    OpTimer timer(l, "rmsnorm", (double)n_rows * x.cols * (x.elem_size() + out.elem_size()), 0);
+    check(fn((const float*)x.data, (int)x.ld, gain ? (const float*)gain->data : nullptr, out.data, (int)out.ld, rows, n_rows,
+             (int)x.cols, eps, code_of(out.dtype), l.stream),
+          "rmsnorm(width=" + std::to_string(x.cols) + ")");
+}
+
+void rmsnorm_add(const Launch& l, const Tensor& y, const Tensor* gain, float eps, float mult, Tensor& x) {
+    if (x.dtype != DType::F32 || y.dtype != DType::F32 || x.rows != y.rows || x.cols != y.cols ||
+        (gain && (gain->dtype != DType::F32 || gain->numel() != x.cols)))
+        throw KernelError("rmsnorm_add: float32 x and y of one shape, float32 gain [width] expected");
+    if (left_out("layernorm")) return;
+    static auto fn = SANDY_KERNEL(rmsnorm, sandy_rmsnorm_add);
+    OpTimer timer(l, "rmsnorm + residual", 3.0 * tensor_bytes(&x), 0);
+    check(fn((const float*)y.data, (int)y.ld, gain ? (const float*)gain->data : nullptr, (float*)x.data, (int)x.ld, (int)x.rows,
+             (int)x.cols, eps, mult, l.stream),
+          "rmsnorm_add(width=" + std::to_string(x.cols) + ")");
+}
+
+void head_norm_gate(const Launch& l, const Tensor& o, const Tensor* gain, const Tensor* gate, GateAct act, float scale,
+                    float eps, int n_heads, Tensor& out) {
+    if (n_heads <= 0 || o.cols % n_heads) throw KernelError("head_norm_gate: the columns do not divide into the heads");
+    const int dim = (int)(o.cols / n_heads);
+    if (o.dtype != DType::F32 || out.rows != o.rows || out.cols != o.cols ||
+        (gain && (gain->dtype != DType::F32 || (gain->numel() != dim && gain->numel() != o.cols))) ||
+        (gate && (gate->rows != o.rows || gate->cols != o.cols)))
+        throw KernelError("head_norm_gate: float32 o [T, H * dim], gain [dim] or [H * dim], gate and out [T, H * dim] expected");
+    static auto fn = SANDY_KERNEL(rmsnorm, sandy_head_norm_gate);
+    OpTimer timer(l, "head norm + gate", tensor_bytes(&o) + tensor_bytes(gate) + tensor_bytes(&out), 0);
+    check(fn((const float*)o.data, (int)o.ld, gain ? (const float*)gain->data : nullptr,
+             gain && gain->numel() == o.cols && n_heads > 1 ? dim : 0, gate ? gate->data : nullptr, gate ? (int)gate->ld : 0,
+             gate ? code_of(gate->dtype) : code_of(out.dtype), out.data, (int)out.ld, code_of(out.dtype), (int)o.rows, n_heads,
+             dim, eps, (int)act, scale, l.stream),
+          "head_norm_gate(H=" + std::to_string(n_heads) + ",dim=" + std::to_string(dim) + ")");
+}
+
+void glu(const Launch& l, const Tensor& a, const Tensor& b, GluAct act, Tensor& out) {
+    if (a.dtype != b.dtype || a.dtype != out.dtype || a.rows != b.rows || a.cols != b.cols || a.ld != b.ld || out.rows != a.rows ||
+        out.cols != a.cols)
+        throw KernelError("glu: a, b and out must agree in shape and type");
+    static auto fn = SANDY_KERNEL(elementwise, sandy_glu);
+    OpTimer timer(l, "gated activation", 3.0 * tensor_bytes(&out), 0);
+    check(fn(a.data, b.data, (int)a.ld, out.data, (int)out.ld, (int)a.rows, (int)a.cols, (int)act, code_of(a.dtype), l.stream), "glu");
+}
+
+void cast_cols(const Launch& l, const Tensor& x, Tensor& out) {
+    if (x.dtype != DType::F32 || out.rows != x.rows || out.cols != x.cols) throw KernelError("cast_cols: float32 x and out of one shape expected");
+    static auto fn = SANDY_KERNEL(elementwise, sandy_cast_cols);
+    OpTimer timer(l, "cast", tensor_bytes(&x) + tensor_bytes(&out), 0);
+    check(fn((const float*)x.data, (int)x.ld, out.data, (int)out.ld, (int)x.rows, (int)x.cols, code_of(out.dtype), l.stream), "cast_cols");
+}
+
+void attention_prepare(const Launch& l, const AttentionPrepare& p, const Tensor& proj, const KVView& c, const int* block_table,
+                       int max_blocks, const int* token_seq, const int* positions, Tensor& q_out) {
+    if (proj.dtype != c.dtype || q_out.dtype != proj.dtype || q_out.rows != proj.rows || q_out.cols != (int64_t)p.n_heads * c.head_dim ||
+        c.n_kv_heads != p.n_kv_heads || c.head_dim < p.qk_dim || c.head_dim < p.v_dim)
+        throw KernelError("attention_prepare: the projection, the queries and the cache disagree");
+    static auto fn = SANDY_KERNEL(attention_prepare, sandy_attention_prepare);
+    OpTimer timer(l, "q/k norm + rotary + cache write", 2.0 * tensor_bytes(&proj), 0);
+    check(fn(proj.data, (int)proj.ld, p.q_off, p.k_off, p.v_off, (int)proj.rows, p.n_heads, p.n_kv_heads, p.qk_dim, p.v_dim,
+             c.head_dim, p.q_gain, p.k_gain, p.eps, p.freq, p.rot_dims, positions, token_seq, block_table, max_blocks, c.k, c.v,
+             c.page_stride, c.page_size, c.num_pages, p.write_cache ? 1 : 0, q_out.data, (int)q_out.ld, p.gate_in, p.ld_gate,
+             p.gate_out, p.gate_scale, code_of(proj.dtype), l.kernel_status, l.stream),
+          "attention_prepare");
+}
+
+// ---- recurrent mixers ------------------------------------------------------------------------------------
+int64_t mlstm_state_floats(int n_heads, int qk_dim, int v_dim) {
+    const int64_t Z = (v_dim + kMatrixStateCols - 1) / kMatrixStateCols;
+    return (int64_t)n_heads * v_dim * qk_dim + (int64_t)n_heads * Z * qk_dim + (int64_t)n_heads * Z;
+}
+
+void delta_prepare(const Launch& l, const StepSeqs& s, const DeltaShape& d, const Tensor& proj, const Tensor& taps,
+                   const Tensor& gates, const float* a_log, const float* dt_bias, const StateView& state, int64_t tail_off,
+                   float q_scale, Tensor& qkv, Tensor& bg) {
+    const int64_t channels = 2 * (int64_t)d.n_qk_heads * d.qk_dim + (int64_t)d.n_heads * d.v_dim;
+    if (proj.cols < channels || taps.dtype != DType::F32 || taps.numel() != channels * d.n_taps || gates.dtype != DType::F32 ||
+        gates.cols < 2 * d.n_heads || qkv.dtype != DType::F32 || qkv.cols != channels || bg.dtype != DType::F32 ||
+        bg.cols != 2 * d.n_heads || !bg.contiguous() || state.dtype != DType::F32)
+        throw KernelError("delta_prepare: shapes disagree");
+    static auto fn = SANDY_KERNEL(matrix_state, sandy_delta_prepare);
+    OpTimer timer(l, "delta rule: conv + norms + gates", tensor_bytes(&proj) + tensor_bytes(&qkv), 0);
+    check(fn(proj.data, (int)proj.ld, code_of(proj.dtype), (const float*)taps.data, d.n_taps, (const float*)gates.data, (int)gates.ld,
+             a_log, dt_bias, (const float*)state.data, state.row_elems, tail_off, s.token_seq, s.q_start, s.seq_slots,
+             (float*)qkv.data, (int)qkv.ld, (float*)bg.data, s.n_tokens, d.n_heads, d.n_qk_heads, d.qk_dim, d.v_dim, q_scale, l.stream),
+          "delta_prepare");
+}
+
+void conv_tail(const Launch& l, const StepSeqs& s, const DeltaShape& d, const Tensor& proj, const StateView& state, int64_t tail_off) {
+    const int64_t channels = 2 * (int64_t)d.n_qk_heads * d.qk_dim + (int64_t)d.n_heads * d.v_dim;
+    static auto fn = SANDY_KERNEL(matrix_state, sandy_conv_tail);
+    OpTimer timer(l, "delta rule: conv tail", 0, 0);
+    check(fn(proj.data, (int)proj.ld, code_of(proj.dtype), (int)channels, d.n_taps, (float*)state.data, state.row_elems, tail_off,
+             s.q_start, s.seq_slots, s.n_seqs, l.stream),
+          "conv_tail");
+}
+
+void delta_scan(const Launch& l, const StepSeqs& s, const DeltaShape& d, const Tensor& qkv, const Tensor& bg, const StateView& state,
+                Tensor& out) {
+    if (out.dtype != DType::F32 || out.cols != (int64_t)d.n_heads * d.v_dim || qkv.dtype != DType::F32)
+        throw KernelError("delta_scan: float32 qkv and out [T, H * e] expected");
+    static auto fn = SANDY_KERNEL(matrix_state, sandy_delta_scan);
+    const double st = 2.0 * s.n_seqs * d.n_heads * d.qk_dim * d.v_dim * 4.0;
+    OpTimer timer(l, "delta rule: recurrence", st + tensor_bytes(&qkv) + tensor_bytes(&out), 6.0 * s.n_tokens * d.n_heads * d.qk_dim * d.v_dim);
+    check(fn((const float*)qkv.data, (int)qkv.ld, (const float*)bg.data, (float*)state.data, state.row_elems, s.q_start, s.seq_slots,
+             (float*)out.data, (int)out.ld, s.n_seqs, d.n_heads, d.n_qk_heads, d.qk_dim, d.v_dim, l.stream),
+          "delta_scan(d=" + std::to_string(d.qk_dim) + ",e=" + std::to_string(d.v_dim) + ")");
+}
+
+void mlstm_scan(const Launch& l, const StepSeqs& s, const MlstmShape& m, const Tensor& proj, const Tensor& gates,
+                const float* gate_bias, const StateView& state, Tensor& out) {
+    if (out.dtype != DType::F32 || out.cols != (int64_t)m.n_heads * m.v_dim || gates.dtype != DType::F32 || gates.cols < 2 * m.n_heads ||
+        state.dtype != DType::F32 || state.row_elems < mlstm_state_floats(m.n_heads, m.qk_dim, m.v_dim))
+        throw KernelError("mlstm_scan: shapes disagree");
+    static auto fn = SANDY_KERNEL(matrix_state, sandy_mlstm_scan);
+    const double st = 2.0 * s.n_seqs * m.n_heads * m.qk_dim * m.v_dim * 4.0;
+    OpTimer timer(l, "matrix memory: recurrence", st + tensor_bytes(&out), 4.0 * s.n_tokens * m.n_heads * m.qk_dim * m.v_dim);
+    check(fn(proj.data, (int)proj.ld, code_of(proj.dtype), m.q_off, m.k_off, m.v_off, (const float*)gates.data, (int)gates.ld, gate_bias,
+             m.cap, m.q_scale, (float*)state.data, state.row_elems, s.q_start, s.seq_slots, (float*)out.data, (int)out.ld, s.n_seqs,
+             m.n_heads, m.qk_dim, m.v_dim, l.stream),
+          "mlstm_scan(d=" + std::to_string(m.qk_dim) + ",e=" + std::to_string(m.v_dim) + ")");
 }
 
 void sample(const Launch& l, const Tensor& logits, int* out_tokens, const float* temperature, const int* top_k,

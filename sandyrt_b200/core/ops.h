@@ -12,6 +12,7 @@
 #include <string>
 #include <vector>
 
+#include "../csrc/matrix_state.h"
 #include "cache.h"
 #include "device.h"
 
@@ -127,10 +128,75 @@ struct AttentionStep {
     // after it, and (query, key) pairs the causal attention looks at
     double kv_tokens = 0, pairs = 0;
 };
+// What some attention layers add to the softmax: a sink per head (float32 [H]: exp(sink) joins the denominator and
+// nothing else) and a factor on each head's output (float32 [T, H], e.g. a sigmoid gate).  Either may be null.
+struct AttentionExtras {
+    const float* sink = nullptr;
+    const float* out_gate = nullptr;
+};
 // Attention of a step's tokens over the cache: picks the kernel for the step's shape.
 void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const KVView& cache, Tensor& out, int n_heads,
-               float scale, int window, Workspace& ws);
+               float scale, int window, Workspace& ws, const AttentionExtras* extras = nullptr);
 int decode_splits(int n_tokens, int n_heads, int max_kv, int sms = 0);
+
+// ---- RMS norms and what goes with them (rmsnorm.cu, elementwise.cu) ------------------------------------------
+// out[r] = x[rows[r] or r] / sqrt(mean(x^2) + eps) * gain; x float32, gain float32 [width] or null.
+void rmsnorm(const Launch& l, const Tensor& x, const Tensor* gain, float eps, Tensor& out, const int* rows, int n_rows);
+// x += mult * y / sqrt(mean(y^2) + eps) * gain; both float32.
+void rmsnorm_add(const Launch& l, const Tensor& y, const Tensor* gain, float eps, float mult, Tensor& x);
+enum class GateAct : int { Sigmoid = 0, Silu = 1 };
+// Per (token, head): out = o / sqrt(mean over the head (o^2) + eps) * gain * act(gate) * scale.  o float32 [T, H * dim];
+// gain float32, [dim] shared by the heads or [H * dim]; gate [T, H * dim] or null.
+void head_norm_gate(const Launch& l, const Tensor& o, const Tensor* gain, const Tensor* gate, GateAct act, float scale,
+                    float eps, int n_heads, Tensor& out);
+enum class GluAct : int { Silu = 0, GeluTanh = 1 };
+// out = act(a) * b, element by element (a and b may be column ranges of one matrix).
+void glu(const Launch& l, const Tensor& a, const Tensor& b, GluAct act, Tensor& out);
+// out = x rounded to out's type (out may be a column range of a wider matrix); x float32.
+void cast_cols(const Launch& l, const Tensor& x, Tensor& out);
+
+// ---- between a q/k/v projection and attention (attention_prepare.cu) -----------------------------------------
+struct AttentionPrepare {
+    int n_heads = 0, n_kv_heads = 0, qk_dim = 0, v_dim = 0;       // the cache's head size is cache.head_dim >= both
+    int q_off = 0, k_off = 0, v_off = 0;                           // first columns of q, k, v in the projection
+    const float* q_gain = nullptr;                                 // RMS norm over the whole q row / k row, or null
+    const float* k_gain = nullptr;
+    float eps = 0.0f;
+    const float* freq = nullptr;                                   // rotary frequencies [rot_dims / 2], or null
+    int rot_dims = 0;
+    const float* gate_in = nullptr;                                // float32 [T, ld_gate]: per-head gate pre-activations
+    int ld_gate = 0;
+    float* gate_out = nullptr;                                     // float32 [T, H]: sigmoid(gate_in) * gate_scale
+    float gate_scale = 1.0f;
+    bool write_cache = true;
+};
+void attention_prepare(const Launch& l, const AttentionPrepare& p, const Tensor& proj, const KVView& cache,
+                       const int* block_table, int max_blocks, const int* token_seq, const int* positions, Tensor& q_out);
+
+// ---- recurrent mixers with a matrix state per head (matrix_state.cu) -------------------------------------------
+// Columns of a head's state that one thread block owns; the matrix memory keeps n and m once per such block.
+constexpr int kMatrixStateCols = SANDY_MATRIX_STATE_COLS;
+int64_t mlstm_state_floats(int n_heads, int qk_dim, int v_dim);
+struct StepSeqs {                                                  // the step's requests, as the recurrences need them
+    int n_tokens = 0, n_seqs = 0;
+    const int* token_seq = nullptr;
+    const int* q_start = nullptr;
+    const int* seq_slots = nullptr;
+};
+struct DeltaShape { int n_heads = 0, n_qk_heads = 0, qk_dim = 0, v_dim = 0, n_taps = 0; };
+// conv + silu + unit vectors + gates.  proj [T, >= channels] (q, k, v channels first); taps float32 [channels, n_taps];
+// gates float32 [T, 2H] (beta's pre-activation, then the decay's); qkv float32 [T, channels]; bg float32 [T, 2H].
+void delta_prepare(const Launch& l, const StepSeqs& s, const DeltaShape& d, const Tensor& proj, const Tensor& taps,
+                   const Tensor& gates, const float* a_log, const float* dt_bias, const StateView& state, int64_t tail_off,
+                   float q_scale, Tensor& qkv, Tensor& bg);
+void conv_tail(const Launch& l, const StepSeqs& s, const DeltaShape& d, const Tensor& proj, const StateView& state,
+               int64_t tail_off);
+void delta_scan(const Launch& l, const StepSeqs& s, const DeltaShape& d, const Tensor& qkv, const Tensor& bg,
+                const StateView& state, Tensor& out);
+struct MlstmShape { int n_heads = 0, qk_dim = 0, v_dim = 0, q_off = 0, k_off = 0, v_off = 0; float cap = 1.0f, q_scale = 1.0f; };
+// gates float32 [T, >= 2H]: input-gate pre-activations, then forget-gate ones; gate_bias float32 [2H].
+void mlstm_scan(const Launch& l, const StepSeqs& s, const MlstmShape& m, const Tensor& proj, const Tensor& gates,
+                const float* gate_bias, const StateView& state, Tensor& out);
 
 // Choose one token per row of float32 `logits`; per-row option arrays may be null.  With `feedback`
 // the drawn token also replaces the row's input token, its position moves on, and the token is

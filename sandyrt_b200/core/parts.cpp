@@ -305,8 +305,9 @@ public:
             ops::kv_append(ctx.launch, k, v, cache, table, ctx.max_blocks, ctx.token_seq, ctx.positions);
         Tensor o = ws.get("attn_out", T, q_cols_, ctx.compute_dtype);
         ops::attention(ctx.launch, ctx.attention_step(cache.group), q, cache, o, n_heads_, scale_, window_, ws);
-        out_.run(ctx, nullptr, &o, x, ops::Act::None, &x);
+        out_.run(ctx, nullptr, &o, x, ops::Act::None, ctx.overwrite ? nullptr : &x);
     }
+    bool can_overwrite() const override { return true; }
 private:
     int64_t width_;
     int n_heads_, n_kv_heads_, head_dim_;
@@ -348,8 +349,9 @@ public:
     void forward(StepContext& ctx, NormedInput& h, Tensor& x) override {
         Tensor g = ctx.workspace->get("ff_inner", h.rows(), inner_, ctx.compute_dtype);
         up_.run(ctx, &h, nullptr, g, act_, nullptr);
-        down_.run(ctx, nullptr, &g, x, ops::Act::None, &x);
+        down_.run(ctx, nullptr, &g, x, ops::Act::None, ctx.overwrite ? nullptr : &x);
     }
+    bool can_overwrite() const override { return true; }
 private:
     int64_t width_, inner_;
     ops::Act act_ = ops::Act::None;
@@ -382,7 +384,7 @@ Table& table() {
     static Table t;
     static std::once_flag once;
     std::call_once(once, [] {
-        for (const char* fam : {"mixer", "feed_forward", "norm", "position", "embedding", "head", "block"}) t[fam];
+        for (const char* fam : {"mixer", "feed_forward", "norm", "position", "embedding", "head", "remix", "block"}) t[fam];
         t["norm"]["layernorm"] = simple<LayerNorm>();
         t["position"]["learned_absolute"] = simple<LearnedAbsolute>();
         t["position"]["none"] = simple<NoPosition>();
@@ -397,6 +399,14 @@ Table& table() {
         };
         t["block"]["pre_norm"] = std::move(pre);
     });
+    // the second group of built-in kinds registers itself through register_part, like any outside kind
+    static std::once_flag more;
+    static thread_local bool entered = false;
+    if (!entered) {
+        entered = true;
+        std::call_once(more, [] { register_hybrid_parts(); });
+        entered = false;
+    }
     return t;
 }
 std::mutex& table_lock() { static std::mutex m; return m; }
@@ -407,7 +417,7 @@ void register_part(const std::string& family, const std::string& kind, PartFacto
     Table& t = table();
     std::lock_guard<std::mutex> g(table_lock());
     auto it = t.find(family);
-    if (it == t.end()) throw ConfigError("unknown part family '" + family + "'; one of mixer, feed_forward, norm, position, embedding, head, block");
+    if (it == t.end()) throw ConfigError("unknown part family '" + family + "'; one of mixer, feed_forward, norm, position, embedding, head, remix, block");
     it->second[kind] = std::move(factory);
 }
 

@@ -17,6 +17,7 @@
 //                     forward(ctx, h, x, call)                 x += mix(h), in place
 //   FeedForward       forward(ctx, h, x)                       x += ff(h), in place
 //   Block             forward(ctx, x, call)                    runs its norms, mixer, feed-forward
+//   Remix             forward(ctx, x, x0)                      x <- f(x, x0), x0 the embedding's output
 //
 // `x` is the residual stream: float32 [tokens, width] in both compute dtypes, so the residual sum is
 // always formed and kept in 32-bit.  `h` is a normed copy in the compute dtype, handed over as a
@@ -61,6 +62,9 @@ struct StepContext {
     Workspace* workspace = nullptr;
     DeviceCaches* caches = nullptr;
     PositionEncoding* position = nullptr;    // the model's position encoding
+    // Set by a block that norms a sublayer's output before it joins the stream: a mixer or feed-forward that
+    // says `can_overwrite()` then writes its result over the tensor it is given instead of adding to it.
+    bool overwrite = false;
     // host copies, for parts that plan their launches on the host
     std::vector<int> host_q_lens, host_kv_before, host_slots;
     int max_q_len = 0, max_kv_len = 0;
@@ -94,6 +98,11 @@ public:
     virtual void forward(StepContext& ctx, const Tensor& x, Tensor& out, const int* rows, int n_rows) = 0;
     // Kernels that can run a LayerNorm inside themselves ask for its parameters here.
     virtual bool layernorm_params(LayerNormParams& out) const { (void)out; return false; }
+    // x += mult * norm(y), both float32: a norm behind a sublayer.  Norms that cannot do this in 32-bit refuse.
+    virtual void forward_add(StepContext& ctx, const Tensor& y, float mult, Tensor& x) {
+        (void)ctx; (void)y; (void)mult; (void)x;
+        throw ConfigError("norm kind '" + spec_.kind + "' cannot follow a sublayer");
+    }
 };
 
 class PositionEncoding : public Part {
@@ -140,12 +149,22 @@ public:
     using Part::Part;
     virtual CacheSpec cache_spec() const { return CacheSpec::none(); }
     virtual void forward(StepContext& ctx, NormedInput& h, Tensor& x, const LayerCall& call) = 0;
+    virtual bool can_overwrite() const { return false; }      // honours StepContext::overwrite
 };
 
 class FeedForward : public Part {
 public:
     using Part::Part;
     virtual void forward(StepContext& ctx, NormedInput& h, Tensor& x) = 0;
+    virtual bool can_overwrite() const { return false; }      // honours StepContext::overwrite
+    virtual bool empty() const { return false; }              // a layer without a feed-forward
+};
+
+// Something that acts on the whole residual stream between layers, with the embedding's output at hand.
+class Remix : public Part {
+public:
+    using Part::Part;
+    virtual void forward(StepContext& ctx, Tensor& x, const Tensor& x0) = 0;
 };
 
 // An arrangement of norms, a mixer and a feed-forward (built from a LayerSpec).
@@ -199,16 +218,21 @@ struct BlockParts {
     std::unique_ptr<FeedForward> feed_forward;
     std::map<std::string, std::unique_ptr<Norm>> norms;
     int64_t width = 0;
+    Json params = Json::object();          // the block's own constants (LayerSpec::block_params)
 };
 struct PartFactory {
     std::function<std::unique_ptr<Part>(const PartSpec&)> make;                // every family but "block"
     std::function<std::unique_ptr<Block>(BlockParts)> make_block;              // "block"
     std::vector<std::string> norm_names;                                       // "block": the norms it wants
 };
-// family: "mixer", "feed_forward", "norm", "position", "embedding", "head" or "block"
+// family: "mixer", "feed_forward", "norm", "position", "embedding", "head", "remix" or "block"
 void register_part(const std::string& family, const std::string& kind, PartFactory factory);
 const PartFactory& get_part(const std::string& family, const std::string& kind);    // unknown -> ConfigError listing the known kinds
 std::vector<std::string> part_kinds(const std::string& family);
+
+// Kinds of parts_hybrid.cpp: RMS norm, gated feed-forward, norms on both sides of a sublayer, attention with a sink
+// beside a matrix memory, the gated delta rule, the re-entry mix of a looped span.  Called once by the registry.
+void register_hybrid_parts();
 
 template <typename T>
 std::unique_ptr<T> make_part(const std::string& family, const PartSpec& spec) {

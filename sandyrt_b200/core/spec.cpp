@@ -79,6 +79,7 @@ Json to_json(const ModelSpec& s) {
     for (const auto& l : s.layers) {
         Json lj = Json::object();
         lj["block"] = l.block;
+        lj["block_params"] = l.block_params.is_object() ? l.block_params : Json::object();
         lj["mixer"] = to_json(l.mixer);
         lj["feed_forward"] = to_json(l.feed_forward);
         Json norms = Json::object();
@@ -93,9 +94,13 @@ Json to_json(const ModelSpec& s) {
         cj["layer"] = c.layer;
         cj["cache"] = c.cache;
         cj["write_cache"] = c.write_cache;
+        if (c.remix >= 0) cj["remix"] = c.remix;
         sched.push(cj);
     }
     j["schedule"] = sched;
+    Json remixes = Json::array();
+    for (const auto& r : s.remixes) remixes.push(to_json(r));
+    j["remixes"] = remixes;
     j["final_norm"] = to_json(s.final_norm);
     j["head"] = to_json(s.head);
     Json prefixes = Json::array();
@@ -136,6 +141,8 @@ ModelSpec model_spec_from_json(const Json& j) {
         for (const Json& lj : j.at("layers").items()) {
             LayerSpec l;
             l.block = lj.at("block").as_string();
+            if (const Json* bp = lj.find("block_params"))
+                if (bp->is_object()) l.block_params = *bp;
             l.mixer = part_spec_from_json(lj.at("mixer"));
             l.feed_forward = part_spec_from_json(lj.at("feed_forward"));
             for (const auto& m : lj.at("norms").members()) l.norms[m.first] = part_spec_from_json(m.second);
@@ -146,8 +153,12 @@ ModelSpec model_spec_from_json(const Json& j) {
             c.layer = (int)cj.at("layer").as_int();
             c.cache = (int)cj.at("cache").as_int();
             if (const Json* w = cj.find("write_cache")) c.write_cache = w->as_bool();
+            if (const Json* r = cj.find("remix"))
+                if (!r->is_null()) c.remix = (int)r->as_int();
             s.schedule.push_back(c);
         }
+        if (const Json* r = j.find("remixes"))
+            for (const Json& v : r->items()) s.remixes.push_back(part_spec_from_json(v));
         s.final_norm = part_spec_from_json(j.at("final_norm"));
         s.head = part_spec_from_json(j.at("head"));
         if (const Json* p = j.find("name_prefixes")) {

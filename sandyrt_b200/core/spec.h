@@ -44,6 +44,7 @@ struct PartSpec {
 // One layer: a block arrangement over a mixer, a feed-forward and their norms.
 struct LayerSpec {
     std::string block;                       // registered block kind, e.g. "pre_norm"
+    Json block_params = Json::object();      // the block's own constants (a residual multiplier, ...)
     PartSpec mixer;
     PartSpec feed_forward;
     std::map<std::string, PartSpec> norms;   // the block kind names the norms it wants
@@ -53,10 +54,13 @@ struct LayerSpec {
 // calls: shared weights).  `cache` names the cache entry the mixer works on.  With `write_cache`
 // false the call appends nothing and only reads what an earlier call of this step wrote there (a
 // layer that reads another layer's keys and values).
+// `remix` >= 0 names an entry of ModelSpec::remixes that runs on the residual stream right before the
+// layer (a model that runs a span of layers several times re-enters the span through one).
 struct LayerCall {
     int layer = 0;
     int cache = 0;
     bool write_cache = true;
+    int remix = -1;
 };
 
 struct ModelSpec {
@@ -68,6 +72,8 @@ struct ModelSpec {
     PartSpec position;
     std::vector<LayerSpec> layers;
     std::vector<LayerCall> schedule;
+    // Parts of family "remix": x <- f(x, x0), x0 being the embedding's output.  Run where the run order says.
+    std::vector<PartSpec> remixes;
     PartSpec final_norm;
     PartSpec head;
     // All names in `tensors` are written without these prefixes; a file may carry one of them on

@@ -98,7 +98,8 @@ paged_attention_kernel(const T* __restrict__ q, int ld_q,
                        const int* __restrict__ token_seq, const int* __restrict__ positions,
                        T* __restrict__ out, int ld_out,
                        int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
-                       float scale, int window, int num_pages, int* __restrict__ status) {
+                       float scale, int window, int num_pages, const float* __restrict__ sink,
+                       const float* __restrict__ out_gate, int* __restrict__ status) {
     __shared__ float q_smem[WARPS_PER_BLOCK][MAX_HEAD_DIM];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long pair = (long long)blockIdx.x * WARPS_PER_BLOCK + warp;
@@ -154,7 +155,9 @@ paged_attention_kernel(const T* __restrict__ q, int ld_q,
         }
         m = m_new;
     }
-    const float inv = 1.0f / l;
+    // a sink adds exp(sink) to the softmax's denominator and nothing to its numerator
+    if (sink) l += expf(sink[h] - m);
+    const float inv = (out_gate ? out_gate[(size_t)t * n_heads + h] : 1.0f) / l;
 #pragma unroll
     for (int i = 0; i < MAX_HEAD_DIM / 32; i++) {
         const int d = lane + 32 * i;
@@ -192,13 +195,14 @@ SANDY_API int sandy_kv_append(const void* k_src, const void* v_src, int ld_src,
 }
 
 // q: [n_tokens, H*D] with row stride ld_q; out: [n_tokens, H*D] with row stride ld_out.
-// window 0 = every earlier key is visible.
-SANDY_API int sandy_paged_attention(const void* q, int ld_q, const void* k_cache, const void* v_cache,
-                                    long long page_stride, const int* block_table, int max_blocks,
-                                    const int* token_seq, const int* positions, void* out, int ld_out,
-                                    int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
-                                    float scale, int window, int num_pages, int dtype, int* status,
-                                    cudaStream_t stream) {
+// window 0 = every earlier key is visible.  sink: float32 [H] or null: exp(sink[h]) joins the softmax's
+// denominator.  out_gate: float32 [n_tokens, H] or null: a factor on each head's output.
+SANDY_API int sandy_paged_attention_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                        long long page_stride, const int* block_table, int max_blocks,
+                                        const int* token_seq, const int* positions, void* out, int ld_out,
+                                        int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                        float scale, int window, int num_pages, int dtype, const float* sink,
+                                        const float* out_gate, int* status, cudaStream_t stream) {
     if (n_tokens == 0) return SANDY_OK;
     if (!q || !k_cache || !v_cache || !block_table || !token_seq || !positions || !out)
         return SANDY_ERR_ARGUMENT;
@@ -211,10 +215,22 @@ SANDY_API int sandy_paged_attention(const void* q, int ld_q, const void* k_cache
     paged_attention_kernel<T><<<blocks, WARPS_PER_BLOCK * 32, 0, stream>>>(                           \
         (const T*)q, ld_q, (const T*)k_cache, (const T*)v_cache, page_stride, block_table, max_blocks, \
         token_seq, positions, (T*)out, ld_out, n_tokens, n_heads, n_kv_heads, head_dim, page_size,    \
-        scale, window, num_pages, status)
+        scale, window, num_pages, sink, out_gate, status)
     if (dtype == SANDY_F32) LAUNCH(float);
     else if (dtype == SANDY_BF16) LAUNCH(bf16);
     else return SANDY_ERR_UNSUPPORTED;
 #undef LAUNCH
     return sandy_launch_status();
+}
+
+// The same without a sink or an output gate.
+SANDY_API int sandy_paged_attention(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                    long long page_stride, const int* block_table, int max_blocks,
+                                    const int* token_seq, const int* positions, void* out, int ld_out,
+                                    int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                    float scale, int window, int num_pages, int dtype, int* status,
+                                    cudaStream_t stream) {
+    return sandy_paged_attention_ext(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, token_seq, positions,
+                                     out, ld_out, n_tokens, n_heads, n_kv_heads, head_dim, page_size, scale, window,
+                                     num_pages, dtype, nullptr, nullptr, status, stream);
 }

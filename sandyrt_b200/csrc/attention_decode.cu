@@ -89,6 +89,15 @@ __device__ __forceinline__ void copy16_async(uint8_t* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
+// The last step of a softmax row: a sink joins the denominator (exp(sink) relative to the row's maximum M,
+// nothing in the numerator), an output gate scales the head's result.
+__device__ __forceinline__ float finish_row(float O, float L, float M, const float* sink, const float* out_gate, int t,
+                                            int h, int n_heads) {
+    if (sink && M > -INFINITY) L += expf(sink[h] - M);
+    const float g = out_gate ? out_gate[(size_t)t * n_heads + h] : 1.0f;
+    return L > 0.0f ? O / L * g : 0.0f;
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(WARPS * 32)
 decode_attention_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k_cache,
@@ -97,7 +106,8 @@ decode_attention_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
                         const int* __restrict__ token_seq, const int* __restrict__ positions,
                         T* __restrict__ out, int ld_out, float* __restrict__ partial_o,
                         float* __restrict__ partial_ml, int n_heads, int n_kv_heads, int page_size,
-                        float scale, int window, int num_splits, int num_pages, int* __restrict__ status) {
+                        float scale, int window, int num_splits, int num_pages, const float* __restrict__ sink,
+                        const float* __restrict__ out_gate, int* __restrict__ status) {
     constexpr int VEC = 16 / sizeof(T);         // elements per 16-byte piece
     constexpr int LPK = D / VEC;                // lanes per key
     constexpr int KPW = 32 / LPK;               // keys per warp per round
@@ -266,7 +276,7 @@ decode_attention_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
             }
         }
         if (num_splits == 1) {
-            out[(size_t)t * ld_out + h * D + d] = from_f32<T>(L > 0.0f ? O / L : 0.0f);
+            out[(size_t)t * ld_out + h * D + d] = from_f32<T>(finish_row(O, L, M, sink, out_gate, t, h, n_heads));
         } else if (partial_o == nullptr) {
             // cluster mode: the splits of this (token, head) are the blocks of one cluster, and each
             // hands its partial state to the first block's shared memory
@@ -301,7 +311,7 @@ decode_attention_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
                         O = fmaf(cl_all[r][d], w, O);
                     }
                 }
-                out[(size_t)t * ld_out + h * D + d] = from_f32<T>(L > 0.0f ? O / L : 0.0f);
+                out[(size_t)t * ld_out + h * D + d] = from_f32<T>(finish_row(O, L, M, sink, out_gate, t, h, n_heads));
             }
         }
     }
@@ -309,7 +319,8 @@ decode_attention_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
 
 template <typename T, int D>
 __global__ void merge_splits_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
-                                    T* __restrict__ out, int ld_out, int n_heads, int num_splits) {
+                                    T* __restrict__ out, int ld_out, int n_heads, int num_splits,
+                                    const float* __restrict__ sink, const float* __restrict__ out_gate) {
     pdl_launch_dependents();
     pdl_wait();
     const int h = blockIdx.x, t = blockIdx.y;
@@ -325,7 +336,7 @@ __global__ void merge_splits_kernel(const float* __restrict__ partial_o, const f
                 O = fmaf(partial_o[(base + i) * D + d], w, O);
             }
         }
-        out[(size_t)t * ld_out + h * D + d] = from_f32<T>(L > 0.0f ? O / L : 0.0f);
+        out[(size_t)t * ld_out + h * D + d] = from_f32<T>(finish_row(O, L, M, sink, out_gate, t, h, n_heads));
     }
 }
 
@@ -333,17 +344,20 @@ template <typename T, int D>
 int launch(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
            const int* block_table, int max_blocks, const int* token_seq, const int* positions, void* out,
            int ld_out, float* scratch, int n_tokens, int n_heads, int n_kv_heads, int page_size, float scale,
-           int window, int num_splits, int num_pages, int* status, cudaStream_t stream) {
+           int window, int num_splits, int num_pages, const float* sink, const float* out_gate, int* status,
+           cudaStream_t stream) {
     float* partial_o = scratch;
     float* partial_ml = scratch ? scratch + (size_t)n_tokens * n_heads * num_splits * D : nullptr;
     dim3 grid(num_splits, n_heads, n_tokens);
     int code = sandy_launch(decode_attention_kernel<T, D>, grid, dim3(WARPS * 32), 0, stream, (const T*)q, ld_q,
                             (const T*)k_cache, (const T*)v_cache, page_stride, block_table, max_blocks, token_seq,
                             positions, (T*)out, ld_out, partial_o, partial_ml, n_heads, n_kv_heads, page_size, scale,
-                            window, num_splits, num_pages, status);
+                            window, num_splits, num_pages, num_splits == 1 ? sink : nullptr,
+                            num_splits == 1 ? out_gate : nullptr, status);
     if (code != 0 || num_splits == 1) return code;
     return sandy_launch(merge_splits_kernel<T, D>, dim3(n_heads, n_tokens), dim3(D < 32 ? 32 : (D > 256 ? 256 : D)), 0,
-                        stream, (const float*)partial_o, (const float*)partial_ml, (T*)out, ld_out, n_heads, num_splits);
+                        stream, (const float*)partial_o, (const float*)partial_ml, (T*)out, ld_out, n_heads, num_splits,
+                        sink, out_gate);
 }
 
 // Cluster form: grid (splits, heads, tokens), clusters of (splits, 1, 1).
@@ -351,7 +365,8 @@ template <typename T, int D>
 int launch_cluster(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
                    const int* block_table, int max_blocks, const int* token_seq, const int* positions, void* out,
                    int ld_out, int n_tokens, int n_heads, int n_kv_heads, int page_size, float scale, int window,
-                   int num_splits, int num_pages, int* status, cudaStream_t stream) {
+                   int num_splits, int num_pages, const float* sink, const float* out_gate, int* status,
+                   cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(num_splits, n_heads, n_tokens);
     cfg.blockDim = dim3(WARPS * 32);
@@ -369,19 +384,20 @@ int launch_cluster(const void* q, int ld_q, const void* k_cache, const void* v_c
     const cudaError_t e = cudaLaunchKernelEx(
         &cfg, decode_attention_kernel<T, D>, (const T*)q, ld_q, (const T*)k_cache, (const T*)v_cache, page_stride,
         block_table, max_blocks, token_seq, positions, (T*)out, ld_out, (float*)nullptr, (float*)nullptr, n_heads,
-        n_kv_heads, page_size, scale, window, num_splits, num_pages, status);
+        n_kv_heads, page_size, scale, window, num_splits, num_pages, sink, out_gate, status);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 }  // namespace
 
 // The cluster form: 2 <= num_splits <= 8, no scratch.  Other arguments as sandy_decode_attention.
-SANDY_API int sandy_decode_attention_cluster(const void* q, int ld_q, const void* k_cache, const void* v_cache,
-                                             long long page_stride, const int* block_table, int max_blocks,
-                                             const int* token_seq, const int* positions, void* out, int ld_out,
-                                             int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
-                                             float scale, int window, int num_splits, int num_pages, int dtype,
-                                             int* status, cudaStream_t stream) {
+SANDY_API int sandy_decode_attention_cluster_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                                 long long page_stride, const int* block_table, int max_blocks,
+                                                 const int* token_seq, const int* positions, void* out, int ld_out,
+                                                 int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                                 float scale, int window, int num_splits, int num_pages, int dtype,
+                                                 const float* sink, const float* out_gate, int* status,
+                                                 cudaStream_t stream) {
     if (n_tokens == 0) return SANDY_OK;
     if (!q || !k_cache || !v_cache || !block_table || !token_seq || !positions || !out) return SANDY_ERR_ARGUMENT;
     if (num_splits < 2 || num_splits > MAX_CLUSTER_SPLITS) return SANDY_ERR_UNSUPPORTED;
@@ -396,7 +412,7 @@ SANDY_API int sandy_decode_attention_cluster(const void* q, int ld_q, const void
     if (dtype == DT && head_dim == DD)                                                                          \
         return launch_cluster<TT, DD>(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, token_seq, \
                                       positions, out, ld_out, n_tokens, n_heads, n_kv_heads, page_size, scale,  \
-                                      window, num_splits, num_pages, status, stream)
+                                      window, num_splits, num_pages, sink, out_gate, status, stream)
     CASE(SANDY_BF16, bf16, 16); CASE(SANDY_BF16, bf16, 32); CASE(SANDY_BF16, bf16, 64);
     CASE(SANDY_BF16, bf16, 128); CASE(SANDY_BF16, bf16, 256);
     CASE(SANDY_F32, float, 16); CASE(SANDY_F32, float, 32); CASE(SANDY_F32, float, 64); CASE(SANDY_F32, float, 128);
@@ -412,12 +428,13 @@ SANDY_API long long sandy_decode_attention_scratch_floats(int n_tokens, int n_he
 
 // q, out: [n_tokens, H*D] (row strides ld_q, ld_out); caches as in attention.cu; scratch: float
 // array of sandy_decode_attention_scratch_floats(...) elements (may be null for one split).
-SANDY_API int sandy_decode_attention(const void* q, int ld_q, const void* k_cache, const void* v_cache,
-                                     long long page_stride, const int* block_table, int max_blocks,
-                                     const int* token_seq, const int* positions, void* out, int ld_out,
-                                     float* scratch, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
-                                     int page_size, float scale, int window, int num_splits, int num_pages,
-                                     int dtype, int* status, cudaStream_t stream) {
+SANDY_API int sandy_decode_attention_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                         long long page_stride, const int* block_table, int max_blocks,
+                                         const int* token_seq, const int* positions, void* out, int ld_out,
+                                         float* scratch, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                         int page_size, float scale, int window, int num_splits, int num_pages,
+                                         int dtype, const float* sink, const float* out_gate, int* status,
+                                         cudaStream_t stream) {
     if (n_tokens == 0) return SANDY_OK;
     if (!q || !k_cache || !v_cache || !block_table || !token_seq || !positions || !out) return SANDY_ERR_ARGUMENT;
     if (num_splits < 1 || (num_splits > 1 && !scratch)) return SANDY_ERR_ARGUMENT;
@@ -432,12 +449,34 @@ SANDY_API int sandy_decode_attention(const void* q, int ld_q, const void* k_cach
     if (dtype == DT && head_dim == DD)                                                                      \
         return launch<TT, DD>(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, token_seq,   \
                               positions, out, ld_out, scratch, n_tokens, n_heads, n_kv_heads, page_size,    \
-                              scale, window, num_splits, num_pages, status, stream)
+                              scale, window, num_splits, num_pages, sink, out_gate, status, stream)
     CASE(SANDY_BF16, bf16, 16); CASE(SANDY_BF16, bf16, 32); CASE(SANDY_BF16, bf16, 64);
     CASE(SANDY_BF16, bf16, 128); CASE(SANDY_BF16, bf16, 256);
     CASE(SANDY_F32, float, 16); CASE(SANDY_F32, float, 32); CASE(SANDY_F32, float, 64); CASE(SANDY_F32, float, 128);
 #undef CASE
     return SANDY_ERR_UNSUPPORTED;
+}
+
+// The two forms above without a sink or an output gate.
+SANDY_API int sandy_decode_attention_cluster(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                             long long page_stride, const int* block_table, int max_blocks,
+                                             const int* token_seq, const int* positions, void* out, int ld_out,
+                                             int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                             float scale, int window, int num_splits, int num_pages, int dtype,
+                                             int* status, cudaStream_t stream) {
+    return sandy_decode_attention_cluster_ext(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, token_seq,
+                                              positions, out, ld_out, n_tokens, n_heads, n_kv_heads, head_dim, page_size,
+                                              scale, window, num_splits, num_pages, dtype, nullptr, nullptr, status, stream);
+}
+SANDY_API int sandy_decode_attention(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                     long long page_stride, const int* block_table, int max_blocks,
+                                     const int* token_seq, const int* positions, void* out, int ld_out,
+                                     float* scratch, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                     int page_size, float scale, int window, int num_splits, int num_pages,
+                                     int dtype, int* status, cudaStream_t stream) {
+    return sandy_decode_attention_ext(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, token_seq, positions,
+                                      out, ld_out, scratch, n_tokens, n_heads, n_kv_heads, head_dim, page_size, scale,
+                                      window, num_splits, num_pages, dtype, nullptr, nullptr, status, stream);
 }
 
 // ---- the entry point that allocates nothing ------------------------------------------------

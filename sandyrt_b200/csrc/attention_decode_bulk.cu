@@ -96,6 +96,15 @@ struct Shape {
     static_assert(NP >= 1 && LPK >= 1 && LPK <= 32 && (32 % LPK) == 0, "head size not supported by this kernel");
 };
 
+// The last step of a softmax row (maxima here are in units of log 2): a sink joins the denominator, nothing in the
+// numerator; an output gate scales the head's result.
+__device__ __forceinline__ float finish_row2(float O, float L, float M, const float* sink, const float* out_gate, int t,
+                                             int h, int n_heads) {
+    if (sink && M > -INFINITY) L += exp2f(sink[h] * 1.4426950408889634f - M);
+    const float g = out_gate ? out_gate[(size_t)t * n_heads + h] : 1.0f;
+    return L > 0.0f ? O / L * g : 0.0f;
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(THREADS)
 decode_attention_bulk_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k_cache,
@@ -104,6 +113,7 @@ decode_attention_bulk_kernel(const T* __restrict__ q, int ld_q, const T* __restr
                              const int* __restrict__ token_seq, const int* __restrict__ positions,
                              T* __restrict__ out, int ld_out, int n_heads, int n_kv_heads, int page_size,
                              float scale, int window, int num_splits, int num_pages, int n_stages,
+                             const float* __restrict__ sink, const float* __restrict__ out_gate,
                              int* __restrict__ status) {
     using S = Shape<T, D>;
     constexpr int VEC = S::VEC, PPL = S::PPL, LPK = S::LPK, KPW = S::KPW, GROUPS = S::GROUPS, EPL = S::EPL;
@@ -303,7 +313,7 @@ decode_attention_bulk_kernel(const T* __restrict__ q, int ld_q, const T* __restr
             }
         }
         if (num_splits == 1) {
-            out[(size_t)t * ld_out + h * D + d] = from_f32<T>(L > 0.0f ? O / L : 0.0f);
+            out[(size_t)t * ld_out + h * D + d] = from_f32<T>(finish_row2(O, L, M, sink, out_gate, t, h, n_heads));
         } else {
             cl_o[d] = O;
             if (d == 0) {
@@ -328,7 +338,7 @@ decode_attention_bulk_kernel(const T* __restrict__ q, int ld_q, const T* __restr
                         O = fmaf(cluster.map_shared_rank(cl_o, r)[d], w, O);
                     }
                 }
-                out[(size_t)t * ld_out + h * D + d] = from_f32<T>(L > 0.0f ? O / L : 0.0f);
+                out[(size_t)t * ld_out + h * D + d] = from_f32<T>(finish_row2(O, L, M, sink, out_gate, t, h, n_heads));
             }
         }
         cluster.sync();
@@ -339,7 +349,7 @@ template <typename T, int D>
 int launch(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
            const int* block_table, int max_blocks, const int* token_seq, const int* positions, void* out,
            int ld_out, int n_tokens, int n_heads, int n_kv_heads, int page_size, float scale, int window,
-           int num_splits, int num_pages, int* status, cudaStream_t stream) {
+           int num_splits, int num_pages, const float* sink, const float* out_gate, int* status, cudaStream_t stream) {
     const size_t stage_bytes = 2 * (size_t)page_size * D * sizeof(T);
     // Many blocks: a short ring each, so that more blocks share an SM (measured on 64 x 12 pairs of
     // 384 keys: 18.8 us with 16 KB, 25.6 us with 32 KB); few blocks: a longer ring each.
@@ -383,7 +393,7 @@ int launch(const void* q, int ld_q, const void* k_cache, const void* v_cache, lo
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, (const T*)q, ld_q, (const T*)k_cache, (const T*)v_cache,
                                              page_stride, block_table, max_blocks, token_seq, positions, (T*)out,
                                              ld_out, n_heads, n_kv_heads, page_size, scale, window, num_splits,
-                                             num_pages, n_stages, status);
+                                             num_pages, n_stages, sink, out_gate, status);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
@@ -397,12 +407,13 @@ SANDY_API int sandy_decode_attention_bulk_ring_bytes(int bytes) {
 }
 
 // Arguments as sandy_decode_attention_cluster (attention_decode.cu); 1 <= num_splits <= 8.
-SANDY_API int sandy_decode_attention_bulk(const void* q, int ld_q, const void* k_cache, const void* v_cache,
-                                          long long page_stride, const int* block_table, int max_blocks,
-                                          const int* token_seq, const int* positions, void* out, int ld_out,
-                                          int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
-                                          float scale, int window, int num_splits, int num_pages, int dtype,
-                                          int* status, cudaStream_t stream) {
+SANDY_API int sandy_decode_attention_bulk_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                              long long page_stride, const int* block_table, int max_blocks,
+                                              const int* token_seq, const int* positions, void* out, int ld_out,
+                                              int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                              float scale, int window, int num_splits, int num_pages, int dtype,
+                                              const float* sink, const float* out_gate, int* status,
+                                              cudaStream_t stream) {
     if (n_tokens == 0) return SANDY_OK;
     if (!q || !k_cache || !v_cache || !block_table || !token_seq || !positions || !out) return SANDY_ERR_ARGUMENT;
     if (num_splits < 1 || num_splits > 8) return SANDY_ERR_UNSUPPORTED;
@@ -418,10 +429,22 @@ SANDY_API int sandy_decode_attention_bulk(const void* q, int ld_q, const void* k
     if (dtype == DT && head_dim == DD)                                                                          \
         return launch<TT, DD>(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, token_seq,       \
                               positions, out, ld_out, n_tokens, n_heads, n_kv_heads, page_size, scale, window,  \
-                              num_splits, num_pages, status, stream)
+                              num_splits, num_pages, sink, out_gate, status, stream)
     CASE(SANDY_BF16, bf16, 16); CASE(SANDY_BF16, bf16, 32); CASE(SANDY_BF16, bf16, 64);
     CASE(SANDY_BF16, bf16, 128); CASE(SANDY_BF16, bf16, 256);
     CASE(SANDY_F32, float, 16); CASE(SANDY_F32, float, 32); CASE(SANDY_F32, float, 64); CASE(SANDY_F32, float, 128);
 #undef CASE
     return SANDY_ERR_UNSUPPORTED;
+}
+
+// The same without a sink or an output gate.
+SANDY_API int sandy_decode_attention_bulk(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                          long long page_stride, const int* block_table, int max_blocks,
+                                          const int* token_seq, const int* positions, void* out, int ld_out,
+                                          int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                          float scale, int window, int num_splits, int num_pages, int dtype,
+                                          int* status, cudaStream_t stream) {
+    return sandy_decode_attention_bulk_ext(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, token_seq,
+                                           positions, out, ld_out, n_tokens, n_heads, n_kv_heads, head_dim, page_size,
+                                           scale, window, num_splits, num_pages, dtype, nullptr, nullptr, status, stream);
 }

@@ -71,12 +71,22 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
+// The last step of a softmax row (maxima here are in units of log 2): a sink joins the denominator, nothing in the
+// numerator; an output gate scales the head's result.
+__device__ __forceinline__ float finish_row2(float O, float L, float M, const float* sink, const float* out_gate, int t,
+                                             int h, int n_heads) {
+    if (sink && M > -INFINITY) L += exp2f(sink[h] * 1.4426950408889634f - M);
+    const float g = out_gate ? out_gate[(size_t)t * n_heads + h] : 1.0f;
+    return L > 0.0f ? O / L * g : 0.0f;
+}
+
 __global__ void __launch_bounds__(WARPS * 32)
 decode_attention_mma_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __restrict__ k_cache,
                             const bf16* __restrict__ v_cache, long long page_stride, const int* __restrict__ block_table,
                             int max_blocks, const int* __restrict__ token_seq, const int* __restrict__ positions,
                             bf16* __restrict__ out, int ld_out, int n_heads, int n_kv_heads, int page_size, float scale,
-                            int window, int num_splits, int num_pages, int* __restrict__ status) {
+                            int window, int num_splits, int num_pages, const float* __restrict__ sink,
+                            const float* __restrict__ out_gate, int* __restrict__ status) {
     // a warp's own stages: [stage][keys | values][16 rows of 128 bytes]
     __shared__ __align__(128) uint8_t st[WARPS][STAGES][2][GROUP_BYTES];
     __shared__ int s_pages[MAX_PAGES];
@@ -291,7 +301,7 @@ decode_attention_mma_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __
             }
         }
         if (!in_cluster) {
-            out[(size_t)t * ld_out + h * D + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+            out[(size_t)t * ld_out + h * D + d] = __float2bfloat16_rn(finish_row2(O, L, M, sink, out_gate, t, h, n_heads));
         } else {
             first_all[split * (D + 2) + d] = O;
             if (d == 0) {
@@ -317,7 +327,7 @@ decode_attention_mma_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __
                         O = fmaf(cl_all[r][d], w, O);
                     }
                 }
-                out[(size_t)t * ld_out + h * D + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+                out[(size_t)t * ld_out + h * D + d] = __float2bfloat16_rn(finish_row2(O, L, M, sink, out_gate, t, h, n_heads));
             }
         }
     }
@@ -334,11 +344,12 @@ SANDY_API int sandy_decode_attention_mma_max_keys(int num_splits, int page_size)
 
 // Arguments as sandy_decode_attention_cluster (attention_decode.cu); bfloat16, heads of 64, 1 <= num_splits <= 8;
 // max_keys: the longest visible range of any token of the launch (checked against the block's table of pages).
-SANDY_API int sandy_decode_attention_mma(const void* q, int ld_q, const void* k_cache, const void* v_cache,
-                                         long long page_stride, const int* block_table, int max_blocks,
-                                         const int* token_seq, const int* positions, void* out, int ld_out, int n_tokens,
-                                         int n_heads, int n_kv_heads, int head_dim, int page_size, float scale, int window,
-                                         int num_splits, int num_pages, int max_keys, int* status, cudaStream_t stream) {
+SANDY_API int sandy_decode_attention_mma_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                             long long page_stride, const int* block_table, int max_blocks,
+                                             const int* token_seq, const int* positions, void* out, int ld_out, int n_tokens,
+                                             int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
+                                             int window, int num_splits, int num_pages, int max_keys, const float* sink,
+                                             const float* out_gate, int* status, cudaStream_t stream) {
     if (n_tokens == 0) return SANDY_OK;
     if (!q || !k_cache || !v_cache || !block_table || !token_seq || !positions || !out) return SANDY_ERR_ARGUMENT;
     if (head_dim != D || num_splits < 1 || num_splits > MAX_CLUSTER_SPLITS) return SANDY_ERR_UNSUPPORTED;
@@ -372,6 +383,17 @@ SANDY_API int sandy_decode_attention_mma(const void* q, int ld_q, const void* k_
     const cudaError_t e = cudaLaunchKernelEx(&cfg, decode_attention_mma_kernel, (const bf16*)q, ld_q, (const bf16*)k_cache,
                                              (const bf16*)v_cache, page_stride, block_table, max_blocks, token_seq, positions,
                                              (bf16*)out, ld_out, n_heads, n_kv_heads, page_size, scale, window, num_splits,
-                                             num_pages, status);
+                                             num_pages, sink, out_gate, status);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}
+
+// The same without a sink or an output gate.
+SANDY_API int sandy_decode_attention_mma(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                         long long page_stride, const int* block_table, int max_blocks,
+                                         const int* token_seq, const int* positions, void* out, int ld_out, int n_tokens,
+                                         int n_heads, int n_kv_heads, int head_dim, int page_size, float scale, int window,
+                                         int num_splits, int num_pages, int max_keys, int* status, cudaStream_t stream) {
+    return sandy_decode_attention_mma_ext(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, token_seq,
+                                          positions, out, ld_out, n_tokens, n_heads, n_kv_heads, head_dim, page_size, scale,
+                                          window, num_splits, num_pages, max_keys, nullptr, nullptr, status, stream);
 }

@@ -82,6 +82,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
                          const int* __restrict__ block_table, int max_blocks, const int* __restrict__ q_start,
                          const int* __restrict__ kv_before, bf16* __restrict__ out, int ld_out, int n_heads,
                          int n_kv_heads, int page_size, float scale, int window, int num_pages,
+                         const float* __restrict__ sink, const float* __restrict__ out_gate,
                          int* __restrict__ status) {
     constexpr int LDS = D + 8;               // row pitch in elements: 16 bytes of padding
     constexpr int CHUNKS = D / 8;            // 16-byte pieces per row
@@ -296,6 +297,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
             const float msafe = m_all == -INFINITY ? 0.0f : m_all;
             const float wa = exp2f(m_run[r] - msafe), wb = exp2f(m_o - msafe);
             l_run[r] = l_run[r] * wa + l_o * wb;
+            m_run[r] = msafe;
 #pragma unroll
             for (int dt = 0; dt < DTILES; dt++) {
                 o[dt][2 * r] = o[dt][2 * r] * wa + src[dt * 4 + 2 * r] * wb;
@@ -305,8 +307,18 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
     }
 
     // ---- write back ----------------------------------------------------------------------
-    const float inv0 = l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f;
-    const float inv1 = l_run[1] > 0.0f ? 1.0f / l_run[1] : 0.0f;
+    // a sink joins the denominator only (maxima here are in units of log 2)
+    if (sink) {
+        const float sk = sink[h] * 1.4426950408889634f;
+        l_run[0] += exp2f(sk - m_run[0]);
+        l_run[1] += exp2f(sk - m_run[1]);
+    }
+    float inv0 = l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f;
+    float inv1 = l_run[1] > 0.0f ? 1.0f / l_run[1] : 0.0f;
+    if (out_gate) {
+        if (row0 < rows_valid) inv0 *= out_gate[(size_t)(qs + t0 + row0) * n_heads + h];
+        if (row1 < rows_valid) inv1 *= out_gate[(size_t)(qs + t0 + row1) * n_heads + h];
+    }
 #pragma unroll
     for (int dt = 0; dt < DTILES; dt++) {
         const int col = h * D + dt * 8 + 2 * t;
@@ -323,7 +335,7 @@ template <int D>
 int launch(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
            const int* block_table, int max_blocks, const int* q_start, const int* kv_before, void* out, int ld_out,
            int n_seqs, int max_q_len, int n_heads, int n_kv_heads, int page_size, float scale, int window,
-           int num_pages, int* status, cudaStream_t stream) {
+           int num_pages, const float* sink, const float* out_gate, int* status, cudaStream_t stream) {
     constexpr int LDS = D + 8;
     const int smem = (BM + 2 * STAGES * BN) * LDS * (int)sizeof(bf16);
     static bool configured = false;
@@ -335,7 +347,7 @@ int launch(const void* q, int ld_q, const void* k_cache, const void* v_cache, lo
     dim3 grid((max_q_len + BM - 1) / BM, n_heads, n_seqs);
     prefill_attention_kernel<D><<<grid, THREADS, smem, stream>>>(
         (const bf16*)q, ld_q, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, block_table, max_blocks, q_start,
-        kv_before, (bf16*)out, ld_out, n_heads, n_kv_heads, page_size, scale, window, num_pages, status);
+        kv_before, (bf16*)out, ld_out, n_heads, n_kv_heads, page_size, scale, window, num_pages, sink, out_gate, status);
     return sandy_launch_status();
 }
 
@@ -343,12 +355,13 @@ int launch(const void* q, int ld_q, const void* k_cache, const void* v_cache, lo
 
 // q, out: bfloat16 [n_tokens, H*D]; q_start: int32 [n_seqs + 1], first new token of each request;
 // kv_before: int32 [n_seqs], tokens each request had in the cache before the step;
-// max_q_len: the longest portion (sizes the grid).  Caches as in attention.cu.
-SANDY_API int sandy_prefill_attention(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+// max_q_len: the longest portion (sizes the grid).  Caches, sink and out_gate as in attention.cu.
+SANDY_API int sandy_prefill_attention_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache,
                                       long long page_stride, const int* block_table, int max_blocks,
                                       const int* q_start, const int* kv_before, void* out, int ld_out, int n_seqs,
                                       int max_q_len, int n_heads, int n_kv_heads, int head_dim, int page_size,
-                                      float scale, int window, int num_pages, int* status, cudaStream_t stream) {
+                                      float scale, int window, int num_pages, const float* sink, const float* out_gate,
+                                      int* status, cudaStream_t stream) {
     if (n_seqs == 0 || max_q_len == 0) return SANDY_OK;
     if (!q || !k_cache || !v_cache || !block_table || !q_start || !kv_before || !out) return SANDY_ERR_ARGUMENT;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || page_size <= 0 || window < 0) return SANDY_ERR_UNSUPPORTED;
@@ -362,8 +375,19 @@ SANDY_API int sandy_prefill_attention(const void* q, int ld_q, const void* k_cac
     if (head_dim == DD)                                                                                         \
         return launch<DD>(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, q_start, kv_before,  \
                           out, ld_out, n_seqs, max_q_len, n_heads, n_kv_heads, page_size, scale, window,        \
-                          num_pages, status, stream)
+                          num_pages, sink, out_gate, status, stream)
     CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
 #undef CASE
     return SANDY_ERR_UNSUPPORTED;
+}
+
+// The same without a sink or an output gate.
+SANDY_API int sandy_prefill_attention(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                      long long page_stride, const int* block_table, int max_blocks,
+                                      const int* q_start, const int* kv_before, void* out, int ld_out, int n_seqs,
+                                      int max_q_len, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                      float scale, int window, int num_pages, int* status, cudaStream_t stream) {
+    return sandy_prefill_attention_ext(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, q_start, kv_before,
+                                       out, ld_out, n_seqs, max_q_len, n_heads, n_kv_heads, head_dim, page_size, scale,
+                                       window, num_pages, nullptr, nullptr, status, stream);
 }

@@ -163,7 +163,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             const int* __restrict__ block_table, int max_blocks, const int* __restrict__ q_start,
                             const int* __restrict__ kv_before, bf16* __restrict__ out, int ld_out, int n_heads,
                             int n_kv_heads, int page_size, float scale, int window, int num_pages,
-                            int use_tma, int* __restrict__ status) {
+                            int use_tma, const float* __restrict__ sink, const float* __restrict__ out_gate,
+                            int* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ int s_table[TABLE_SMEM];
     __shared__ int s_run[RUNS_SMEM];    // per key tile: its first page if TMA fetches it, else -1
@@ -486,8 +487,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         tmem_wait_ld();
         bar_sync(BAR_MAX, SOFTMAX_THREADS);
         if (row < rows_valid) {
-            const float l = l_run + s_sum[half ^ 1][row];
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            float l = l_run + s_sum[half ^ 1][row];
+            // a sink joins the denominator only; the row's exponentials refer to m_ref (both halves agree on it)
+            if (sink) l += ex2(sink[h] * 1.4426950408889634f - (m_ref == -INFINITY ? 0.0f : m_ref) * scale_log2);
+            float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            if (out_gate) inv *= out_gate[(size_t)(qs + t0 + row) * n_heads + h];
             bf16* dst = out + (size_t)(qs + t0 + row) * ld_out + h * HD + half * 32;
 #pragma unroll
             for (int g = 0; g < 4; g++) {
@@ -553,11 +557,12 @@ bool get_page_map(const void* cache, long long page_stride, int num_pages, int n
 // Arguments as sandy_prefill_attention (attention_prefill.cu).  Heads of 64 only; out and q rows
 // must be 16-byte aligned.  SANDY_ERR_UNSUPPORTED for everything else: the caller then takes the
 // mma.sync kernel.
-SANDY_API int sandy_prefill_attention_tc(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+SANDY_API int sandy_prefill_attention_tc_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache,
                                          long long page_stride, const int* block_table, int max_blocks,
                                          const int* q_start, const int* kv_before, void* out, int ld_out, int n_seqs,
                                          int max_q_len, int n_heads, int n_kv_heads, int head_dim, int page_size,
-                                         float scale, int window, int num_pages, int* status, cudaStream_t stream) {
+                                         float scale, int window, int num_pages, const float* sink,
+                                         const float* out_gate, int* status, cudaStream_t stream) {
     if (n_seqs == 0 || max_q_len == 0) return SANDY_OK;
     if (!q || !k_cache || !v_cache || !block_table || !q_start || !kv_before || !out) return SANDY_ERR_ARGUMENT;
     if (head_dim != HD) return SANDY_ERR_UNSUPPORTED;
@@ -589,5 +594,16 @@ SANDY_API int sandy_prefill_attention_tc(const void* q, int ld_q, const void* k_
     return sandy_launch(prefill_attention_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, mk, mv, (const bf16*)q, ld_q,
                         (const bf16*)k_cache, (const bf16*)v_cache, page_stride, block_table, max_blocks, q_start,
                         kv_before, (bf16*)out, ld_out, n_heads, n_kv_heads, page_size, scale, window, num_pages, use_tma,
-                        status);
+                        sink, out_gate, status);
+}
+
+// The same without a sink or an output gate.
+SANDY_API int sandy_prefill_attention_tc(const void* q, int ld_q, const void* k_cache, const void* v_cache,
+                                         long long page_stride, const int* block_table, int max_blocks,
+                                         const int* q_start, const int* kv_before, void* out, int ld_out, int n_seqs,
+                                         int max_q_len, int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                         float scale, int window, int num_pages, int* status, cudaStream_t stream) {
+    return sandy_prefill_attention_tc_ext(q, ld_q, k_cache, v_cache, page_stride, block_table, max_blocks, q_start,
+                                          kv_before, out, ld_out, n_seqs, max_q_len, n_heads, n_kv_heads, head_dim,
+                                          page_size, scale, window, num_pages, nullptr, nullptr, status, stream);
 }

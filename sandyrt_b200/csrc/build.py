@@ -47,6 +47,10 @@ LIBRARIES: Dict[str, List[str]] = {
     "attention_prefill": [],
     "attention_prefill_tc": [],
     "sampling": [],
+    "rmsnorm": [],
+    "elementwise": [],
+    "attention_prepare": [],
+    "matrix_state": [],
 }
 
 
@@ -205,8 +209,9 @@ def _core_hash() -> str:
         with open(os.path.join(CORE_DIR, fname), "rb") as f:
             h.update(fname.encode())
             h.update(f.read())
-    with open(os.path.join(CSRC_DIR, "sandy_kernels.h"), "rb") as f:
-        h.update(f.read())
+    for shared in ("sandy_kernels.h", "matrix_state.h"):
+        with open(os.path.join(CSRC_DIR, shared), "rb") as f:
+            h.update(f.read())
     h.update(" ".join(CXX_FLAGS + LINK_FLAGS).encode())
     return h.hexdigest()
 

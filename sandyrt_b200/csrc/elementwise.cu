@@ -1,0 +1,84 @@
+// Small element-wise kernels between the products of a layer.
+//
+//   sandy_glu         out[t, j] = act(a[t, j]) * b[t, j]     a gated feed-forward's inner activation: a and b are the
+//                                                            two halves of one fused up-projection
+//   sandy_cast_cols   out[t, c0 + j] = x[t, j]               float32 rows rounded into a column range of a wider matrix
+//                                                            of the compute type (the operand [x; x0] of a product
+//                                                            over two streams side by side)
+//
+// The activation is computed in 32-bit and the result rounded once.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float act_of(float z, int act) {
+    if (act == 0) return z / (1.0f + expf(-z));                                         // silu
+    if (act == 1) {                                                                     // gelu, tanh form
+        const float u = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+        return 0.5f * z * (1.0f + tanhf(u));
+    }
+    return z;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+glu_kernel(const T* __restrict__ a, const T* __restrict__ b, int ld_in, T* __restrict__ out, int ld_out, int rows, int cols,
+           int act) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long long n = (long long)rows * cols;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / cols, j = i % cols;
+        const float g = to_f32(a[t * ld_in + j]), u = to_f32(b[t * ld_in + j]);
+        out[t * ld_out + j] = from_f32<T>(act_of(g, act) * u);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+cast_cols_kernel(const float* __restrict__ x, int ldx, T* __restrict__ out, int ld_out, int rows, int cols) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long long n = (long long)rows * cols;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / cols, j = i % cols;
+        out[t * ld_out + j] = from_f32<T>(x[t * ldx + j]);
+    }
+}
+
+inline unsigned blocks_for(long long n) {
+    const long long want = (n + 255) / 256;
+    const long long cap = (long long)sandy_sm_count() * 16;
+    return (unsigned)(want < 1 ? 1 : (want > cap ? cap : want));
+}
+
+}  // namespace
+
+// a, b: [rows, cols] of dtype with the same pitch ld_in; out: [rows, cols] of dtype.  act: 0 silu, 1 gelu (tanh).
+SANDY_API int sandy_glu(const void* a, const void* b, int ld_in, void* out, int ld_out, int rows, int cols, int act, int dtype,
+                        cudaStream_t stream) {
+    if (rows == 0 || cols == 0) return SANDY_OK;
+    if (!a || !b || !out) return SANDY_ERR_ARGUMENT;
+    const unsigned grid = blocks_for((long long)rows * cols);
+    if (dtype == SANDY_F32)
+        return sandy_launch(glu_kernel<float>, dim3(grid), dim3(256), 0, stream, (const float*)a, (const float*)b, ld_in,
+                            (float*)out, ld_out, rows, cols, act);
+    if (dtype == SANDY_BF16)
+        return sandy_launch(glu_kernel<bf16>, dim3(grid), dim3(256), 0, stream, (const bf16*)a, (const bf16*)b, ld_in,
+                            (bf16*)out, ld_out, rows, cols, act);
+    return SANDY_ERR_UNSUPPORTED;
+}
+
+// x: float32 [rows, cols] with pitch ldx; out: rows of out_dtype with pitch ld_out (the caller passes the address of
+// the first column to fill).
+SANDY_API int sandy_cast_cols(const float* x, int ldx, void* out, int ld_out, int rows, int cols, int out_dtype,
+                              cudaStream_t stream) {
+    if (rows == 0 || cols == 0) return SANDY_OK;
+    if (!x || !out) return SANDY_ERR_ARGUMENT;
+    const unsigned grid = blocks_for((long long)rows * cols);
+    if (out_dtype == SANDY_F32)
+        return sandy_launch(cast_cols_kernel<float>, dim3(grid), dim3(256), 0, stream, x, ldx, (float*)out, ld_out, rows, cols);
+    if (out_dtype == SANDY_BF16)
+        return sandy_launch(cast_cols_kernel<bf16>, dim3(grid), dim3(256), 0, stream, x, ldx, (bf16*)out, ld_out, rows, cols);
+    return SANDY_ERR_UNSUPPORTED;
+}

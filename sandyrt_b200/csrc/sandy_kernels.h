@@ -9,6 +9,8 @@
 
 #include <cuda_runtime.h>
 
+#include "matrix_state.h"
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -99,6 +101,83 @@ int sandy_prefill_attention_tc(const void* q, int ld_q, const void* k_cache, con
                                const int* block_table, int max_blocks, const int* q_start, const int* kv_before, void* out,
                                int ld_out, int n_seqs, int max_q_len, int n_heads, int n_kv_heads, int head_dim,
                                int page_size, float scale, int window, int num_pages, int* status, cudaStream_t stream);
+
+/* the attention kernels with a sink per head (float32 [H]: exp(sink) joins the softmax's denominator) and a factor on
+   each head's output (float32 [T, H]); either may be null.  The entry points above are these with both null. */
+int sandy_paged_attention_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+                              const int* block_table, int max_blocks, const int* token_seq, const int* positions, void* out,
+                              int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
+                              int window, int num_pages, int dtype, const float* sink, const float* out_gate, int* status,
+                              cudaStream_t stream);
+int sandy_decode_attention_cluster_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+                                       const int* block_table, int max_blocks, const int* token_seq, const int* positions,
+                                       void* out, int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                       int page_size, float scale, int window, int num_splits, int num_pages, int dtype,
+                                       const float* sink, const float* out_gate, int* status, cudaStream_t stream);
+int sandy_decode_attention_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+                               const int* block_table, int max_blocks, const int* token_seq, const int* positions, void* out,
+                               int ld_out, float* scratch, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                               int page_size, float scale, int window, int num_splits, int num_pages, int dtype,
+                               const float* sink, const float* out_gate, int* status, cudaStream_t stream);
+int sandy_decode_attention_mma_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+                                   const int* block_table, int max_blocks, const int* token_seq, const int* positions,
+                                   void* out, int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                   int page_size, float scale, int window, int num_splits, int num_pages, int max_keys,
+                                   const float* sink, const float* out_gate, int* status, cudaStream_t stream);
+int sandy_decode_attention_bulk_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+                                    const int* block_table, int max_blocks, const int* token_seq, const int* positions,
+                                    void* out, int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                    int page_size, float scale, int window, int num_splits, int num_pages, int dtype,
+                                    const float* sink, const float* out_gate, int* status, cudaStream_t stream);
+int sandy_prefill_attention_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+                                const int* block_table, int max_blocks, const int* q_start, const int* kv_before, void* out,
+                                int ld_out, int n_seqs, int max_q_len, int n_heads, int n_kv_heads, int head_dim,
+                                int page_size, float scale, int window, int num_pages, const float* sink,
+                                const float* out_gate, int* status, cudaStream_t stream);
+int sandy_prefill_attention_tc_ext(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+                                   const int* block_table, int max_blocks, const int* q_start, const int* kv_before,
+                                   void* out, int ld_out, int n_seqs, int max_q_len, int n_heads, int n_kv_heads,
+                                   int head_dim, int page_size, float scale, int window, int num_pages, const float* sink,
+                                   const float* out_gate, int* status, cudaStream_t stream);
+
+/* attention_prepare.cu */
+int sandy_attention_prepare(const void* proj, int ld, int q_off, int k_off, int v_off, int n_tokens, int n_heads,
+                            int n_kv_heads, int qk_dim, int v_dim, int pad_dim, const float* q_gain, const float* k_gain,
+                            float eps, const float* freq, int rot_dims, const int* positions, const int* token_seq,
+                            const int* block_table, int max_blocks, void* k_cache, void* v_cache, long long page_stride,
+                            int page_size, int num_pages, int write_cache, void* q_out, int ld_q, const float* gate_in,
+                            int ld_gate, float* gate_out, float gate_scale, int dtype, int* status, cudaStream_t stream);
+
+/* rmsnorm.cu */
+int sandy_rmsnorm(const float* x, int ldx, const float* gain, void* out, int ldo, const int* rows, int n_rows, int width,
+                  float eps, int out_dtype, cudaStream_t stream);
+int sandy_rmsnorm_add(const float* y, int ldy, const float* gain, float* x, int ldx, int n_rows, int width, float eps,
+                      float mult, cudaStream_t stream);
+int sandy_head_norm_gate(const float* o, int ldo, const float* gain, int gain_stride, const void* gate, int ldg,
+                         int gate_dtype, void* out, int ld_out, int out_dtype, int n_tokens, int n_heads, int dim, float eps,
+                         int act, float scale, cudaStream_t stream);
+
+/* elementwise.cu */
+int sandy_glu(const void* a, const void* b, int ld_in, void* out, int ld_out, int rows, int cols, int act, int dtype,
+              cudaStream_t stream);
+int sandy_cast_cols(const float* x, int ldx, void* out, int ld_out, int rows, int cols, int out_dtype, cudaStream_t stream);
+
+/* matrix_state.cu */
+long long sandy_mlstm_state_floats(int n_heads, int qk_dim, int v_dim);
+int sandy_delta_prepare(const void* proj, int ld, int dtype, const float* taps, int n_taps, const float* gates, int ld_gates,
+                        const float* a_log, const float* dt_bias, const float* state, long long state_stride,
+                        long long tail_off, const int* token_seq, const int* q_start, const int* seq_slots, float* qkv,
+                        int ld_qkv, float* bg, int n_tokens, int n_heads, int n_qk_heads, int qk_dim, int v_dim,
+                        float q_scale, cudaStream_t stream);
+int sandy_conv_tail(const void* proj, int ld, int dtype, int channels, int n_taps, float* state, long long state_stride,
+                    long long tail_off, const int* q_start, const int* seq_slots, int n_seqs, cudaStream_t stream);
+int sandy_delta_scan(const float* qkv, int ld, const float* bg, float* state, long long state_stride, const int* q_start,
+                     const int* seq_slots, float* out, int ld_out, int n_seqs, int n_heads, int n_qk_heads, int qk_dim,
+                     int v_dim, cudaStream_t stream);
+int sandy_mlstm_scan(const void* proj, int ld, int dtype, int q_off, int k_off, int v_off, const float* gates, int ld_gates,
+                     const float* gate_bias, float cap, float q_scale, float* state, long long state_stride,
+                     const int* q_start, const int* seq_slots, float* out, int ld_out, int n_seqs, int n_heads, int qk_dim,
+                     int v_dim, cudaStream_t stream);
 
 /* sampling.cu */
 int sandy_sample(const float* logits, int ld, int n_rows, int vocab, const float* temperature, const int* top_k,

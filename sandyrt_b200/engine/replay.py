@@ -24,7 +24,7 @@ import sys
 from typing import List, Optional
 
 DTYPES = {"bfloat16": "bfloat16", "bf16": "bfloat16", "float32": "float32", "fp32": "float32"}
-MAX_LIVE_REQUESTS = 64
+MAX_LIVE_REQUESTS = 4         # state slots of the engine: no more requests are live at any time
 
 
 def _round_up(n: int, m: int) -> int:
@@ -32,7 +32,7 @@ def _round_up(n: int, m: int) -> int:
 
 
 def run(model_dir: str, dtype_name: str, out_dir: str, max_tokens: int, lines,
-        page_size: int = 16, log=sys.stdout) -> int:
+        page_size: int = 16, log=sys.stdout, max_requests: int = MAX_LIVE_REQUESTS) -> int:
     import torch
 
     from ..models.model import load_model
@@ -45,7 +45,7 @@ def run(model_dir: str, dtype_name: str, out_dir: str, max_tokens: int, lines,
     model = load_model(model_dir, device="cuda:0", dtype=dtype)
     # The pool holds `max_tokens` tokens, in whole pages.
     engine = Engine(model, max_tokens=_round_up(max_tokens, page_size), page_size=page_size,
-                    max_requests=MAX_LIVE_REQUESTS)
+                    max_requests=max_requests)
     for raw in lines:
         raw = raw.strip()
         if not raw:
@@ -83,8 +83,11 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (sizes the cache pool)")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (power of two)")
+    ap.add_argument("--max-requests", type=int, default=MAX_LIVE_REQUESTS,
+                    help="state slots: the most requests that are live at any time")
     args = ap.parse_args(argv)
-    return run(args.model, args.dtype, args.out, args.max_tokens, sys.stdin, page_size=args.page_size)
+    return run(args.model, args.dtype, args.out, args.max_tokens, sys.stdin, page_size=args.page_size,
+               max_requests=args.max_requests)
 
 
 if __name__ == "__main__":

@@ -45,6 +45,7 @@ class LayerSpec:
     mixer: PartSpec
     feed_forward: PartSpec
     norms: Dict[str, PartSpec]       # the block kind names the norms it wants
+    block_params: Dict[str, Any] = dataclasses.field(default_factory=dict)     # the block's own constants
 
 
 @dataclasses.dataclass(frozen=True)
@@ -58,6 +59,8 @@ class LayerCall:
     layer: int
     cache: int
     write_cache: bool = True
+    # index into ModelSpec.remixes of a part that runs on the residual stream right before the layer
+    remix: Optional[int] = None
 
 
 @dataclasses.dataclass(frozen=True)
@@ -79,6 +82,8 @@ class ModelSpec:
     # such as a stored causal mask).
     ignored_tensors: Tuple[str, ...] = ()
     eos_token_id: Optional[int] = None
+    # parts of family "remix": x <- f(x, embedding output), run where the run order names them
+    remixes: Sequence[PartSpec] = ()
 
     def n_caches(self) -> int:
         return 1 + max((c.cache for c in self.schedule), default=-1)
@@ -89,8 +94,11 @@ class ModelSpec:
             "max_positions": self.max_positions, "embedding": self.embedding.to_json(),
             "position": self.position.to_json(),
             "layers": [{"block": l.block, "mixer": l.mixer.to_json(), "feed_forward": l.feed_forward.to_json(),
-                        "norms": {k: v.to_json() for k, v in l.norms.items()}} for l in self.layers],
-            "schedule": [{"layer": c.layer, "cache": c.cache, "write_cache": c.write_cache} for c in self.schedule],
+                        "norms": {k: v.to_json() for k, v in l.norms.items()},
+                        "block_params": dict(l.block_params)} for l in self.layers],
+            "schedule": [dict({"layer": c.layer, "cache": c.cache, "write_cache": c.write_cache},
+                              **({} if c.remix is None else {"remix": c.remix})) for c in self.schedule],
+            "remixes": [r.to_json() for r in self.remixes],
             "final_norm": self.final_norm.to_json(), "head": self.head.to_json(),
             "name_prefixes": list(self.name_prefixes), "ignored_tensors": list(self.ignored_tensors),
             "eos_token_id": self.eos_token_id,
@@ -103,8 +111,10 @@ class ModelSpec:
             max_positions=j.get("max_positions"), embedding=PartSpec.from_json(j["embedding"]),
             position=PartSpec.from_json(j["position"]),
             layers=[LayerSpec(l["block"], PartSpec.from_json(l["mixer"]), PartSpec.from_json(l["feed_forward"]),
-                              {k: PartSpec.from_json(v) for k, v in l["norms"].items()}) for l in j["layers"]],
-            schedule=[LayerCall(c["layer"], c["cache"], c.get("write_cache", True)) for c in j["schedule"]],
+                              {k: PartSpec.from_json(v) for k, v in l["norms"].items()},
+                              dict(l.get("block_params") or {})) for l in j["layers"]],
+            schedule=[LayerCall(c["layer"], c["cache"], c.get("write_cache", True), c.get("remix")) for c in j["schedule"]],
+            remixes=tuple(PartSpec.from_json(r) for r in j.get("remixes") or ()),
             final_norm=PartSpec.from_json(j["final_norm"]), head=PartSpec.from_json(j["head"]),
             name_prefixes=tuple(j.get("name_prefixes") or ("",)), ignored_tensors=tuple(j.get("ignored_tensors") or ()),
             eos_token_id=j.get("eos_token_id"))

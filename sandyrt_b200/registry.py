@@ -39,8 +39,9 @@ _KEEP: List[Any] = []            # callbacks and strings the library holds point
 
 def _builtin_config_classes() -> Dict[str, Type[ModelConfig]]:
     from .config.gpt2 import GPT2Config
+    from .config.panupel import PanupelConfig
 
-    return {GPT2Config.architecture: GPT2Config}
+    return {GPT2Config.architecture: GPT2Config, PanupelConfig.architecture: PanupelConfig}
 
 
 def _text(s: str) -> int:
