@@ -4,6 +4,7 @@
     python bench.py --workload medium|xl          the mixed-batch workloads through LLM.generate
     python bench.py --profile-kernels             time per kernel class of a decode and a prompt step
     python bench.py --attribute [--batch B]       what each family of launches costs inside a step (leave-one-out)
+    python bench.py --hybrid [--batch B]          Panupel beside GPT-2 at equal layer sizes: throughput, time per kernel class
     python bench.py --micro gemm|decode-attention|prefill-attention [...]   kernel micro-benchmarks
 
 Default workload: GPT-2 small (12 layers, width 768, 12 heads of 64, inner 3072, vocabulary 50257,
@@ -365,6 +366,22 @@ def profile_kernels(dtype_name: str, layers: int, batch: int, size: str = "small
 
     raw = load_model_config(size)
     model, cfg = make_model(raw, layers or raw["n_layer"], dtype_name)
+    return kernel_table(cfg, dtype_name, batch, model)
+
+
+def kernel_table(cfg, dtype_name: str, batch: int, model=None) -> int:
+    """The table of profile_kernels for any configuration (random weights unless a bound model is given)."""
+    import numpy as np
+    import torch
+
+    from sandyrt_b200 import core
+    from sandyrt_b200.engine.step import Engine, StepEntry
+    from sandyrt_b200.models.model import build_model
+
+    if model is None:
+        model = build_model(cfg)
+        model.bind_random(0, getattr(torch, dtype_name))
+    n_layers = len(model.spec.schedule)
     engine = Engine(model, max_tokens=batch * 512 + 4096, max_requests=max(batch, 2), max_step_tokens=4096,
                     use_cuda_graphs=False)
     rng = np.random.default_rng(0)
@@ -388,13 +405,78 @@ def profile_kernels(dtype_name: str, layers: int, batch: int, size: str = "small
             fn(k)
         table = core.call("global", None, "profile_kernels", enable=False)
         total = sum(r["us"] for r in table) / reps
-        print(f"{what} ({dtype_name}, {cfg.n_layer} layers): {total:.1f} us in kernels per step")
+        print(f"{what} ({dtype_name}, {n_layers} layers): {total:.1f} us in kernels per step")
         print("  class                     calls      us   share    GB/s  TFLOP/s")
         for r in sorted(table, key=lambda r: -r["us"]):
             us = r["us"] / reps
             gbs = r["bytes"] / reps / us / 1e3 if us else 0.0
             tf = r["flops"] / reps / us / 1e6 if us else 0.0
             print(f"  {r['class']:24s} {r['calls'] // reps:6d} {us:7.1f} {100 * us / total:6.1f}% {gbs:7.0f} {tf:8.1f}")
+    return 0
+
+
+# ---- the hybrid design beside GPT-2 at equal size -------------------------------------------------------
+# Layer sizes that resemble real models: width, heads of 64, an inner size that gives the gated feed-forward the
+# parameter count of GPT-2's plain one (three matrices of 8/3 x width against two of 4 x width).
+HYBRID_SIZES = {
+    "768": dict(width=768, heads=12, kv_heads=4, ff=2048),
+    "1536": dict(width=1536, heads=24, kv_heads=8, ff=4096),
+}
+
+
+def hybrid_config(width, heads, kv_heads, ff, vocab=50257, layers=4):
+    """`layers` layers, delta and parallel in turn, the parallel layer's heads split between its two mixers."""
+    delta = {"type": "delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "conv": 4},
+             "mlp": {"kind": "dense", "ff": ff}}
+    par = {"type": "parallel", "mlp": {"kind": "dense", "ff": ff},
+           "mixer": {"left": {"heads": heads // 2, "kv_heads": max(kv_heads // 2, 1), "dim": 64, "vdim": 64, "scale": 0.125,
+                              "rot": {"dims": 64, "base": 10000.0}},
+                     "right": {"heads": heads // 4, "dim": 64, "vdim": 128, "gate_cap": 12.0}, "left_scale": 1.0, "right_scale": 1.0}}
+    return {"architecture": "Panupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 1.0,
+            "layers": [delta if i % 2 == 0 else par for i in range(layers)]}
+
+
+def hybrid(dtype_name: str, layers: int, batch: int, steps: int, warmup: int) -> int:
+    """Prefill and decode throughput of Panupel at sizes that resemble real layers, beside GPT-2 with the same width,
+    heads, layer count and vocabulary, both with random weights; then the device time per kernel class of both, so
+    that like kernels can be held against each other.  One JSON line per size, then the tables."""
+    import numpy as np
+    import torch
+
+    from sandyrt_b200.config.base import config_from_normalised
+    from sandyrt_b200.engine.llm import LLM
+    from sandyrt_b200.models.model import build_model
+
+    peaks = load_peaks()
+    layers = layers or 4
+    rng = np.random.default_rng(0)
+    for name, sz in HYBRID_SIZES.items():
+        gpt2_raw = {**load_model_config("small"), "n_embd": sz["width"], "n_head": sz["heads"], "n_inner": None, "n_layer": layers}
+        out = {"size": name, "layers": layers, "dtype": dtype_name, "data": "synthetic", "peaks": peaks["source"]}
+        for arch, raw in (("panupel", hybrid_config(layers=layers, **sz)), ("gpt2", gpt2_raw)):
+            cfg = config_from_normalised(raw)
+            cfg.validate()
+            model = build_model(cfg)
+            model.bind_random(0, getattr(torch, dtype_name))
+            llm = LLM(model, cache_tokens=16 * 1024 + 4096, max_live=16, max_step_tokens=4096, prefill_chunk_tokens=2048)
+            vocab = cfg.vocab_size
+            row = {"weight_bytes": model.weight_bytes()}
+            for b in (1, batch):
+                ms, _, ctx, launches = decode_run(llm, b, 128, steps, max(warmup, 3), rng, vocab, want_e2e=False)
+                moved = model.weight_bytes() + llm.engine.cache.kv_bytes_per_token() * b * ctx
+                row[f"decode_b{b}"] = {"tokens_per_s": b / (ms / 1e3), "ms_per_step": ms, "mean_context": round(ctx, 1),
+                                       "launches_per_step": launches, "hbm_frac": moved / (ms / 1e3) / 1e9 / peaks["hbm_gbs"]}
+            pf_ms, pf_host = prefill_run(llm.engine, vocab, rng)
+            row["prefill_2x1024"] = {"tokens_per_s": 2048 / (pf_ms / 1e3), "ms": pf_ms, "ms_with_host": pf_host}
+            out[arch] = row
+            del llm, model
+        print(json.dumps(out), flush=True)
+    # per kernel class, eager launches with events around each
+    for name, sz in HYBRID_SIZES.items():
+        gpt2_raw = {**load_model_config("small"), "n_embd": sz["width"], "n_head": sz["heads"], "n_inner": None, "n_layer": layers}
+        for arch, raw in (("panupel", hybrid_config(layers=layers, **sz)), ("gpt2", gpt2_raw)):
+            print(f"---- {arch}, width {name} ----")
+            kernel_table(config_from_normalised(raw), dtype_name, batch)
     return 0
 
 
@@ -416,6 +498,8 @@ def main() -> int:
     ap.add_argument("--attribute", action="store_true", help="print what each family of launches costs inside a step instead")
     ap.add_argument("--size", default="small", choices=["small", "medium", "xl"], help="model size of --attribute / --profile-kernels")
     ap.add_argument("--attribute-prompts", default="2x1024", help="the prompt step of --attribute: requests x tokens")
+    ap.add_argument("--hybrid", action="store_true",
+                    help="Panupel beside GPT-2 at equal sizes: decode and prefill throughput, then time per kernel class")
     ap.add_argument("--micro", nargs=argparse.REMAINDER, help="run a kernel micro-benchmark (see sandyrt_b200/csrc/microbench.py)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -426,6 +510,8 @@ def main() -> int:
     if args.micro is not None:
         from sandyrt_b200.csrc import microbench
         return microbench.main(args.micro)
+    if args.hybrid:
+        return hybrid(args.dtype, args.layers, args.batch, min(args.steps, 128), args.warmup)
     if args.workload:
         return workload(args.workload, args.dtype, args.layers)
     if args.profile_kernels:

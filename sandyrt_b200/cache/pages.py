@@ -26,7 +26,7 @@ from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 from .. import core
 from ..errors import CacheError, NoFreeSlot, OutOfPages  # noqa: F401  (re-exported)
-from ..parts.base import PagedKVSpec, StateSpec, cache_spec_json
+from ..parts.base import PagedKVSpec, PagedStateSpec, StateSpec, cache_spec_json
 
 FREED = -1   # entry of a block list whose page has been given back (window has passed it)
 
@@ -102,7 +102,7 @@ class CacheLayout:
     @classmethod
     def from_specs(cls, specs: Sequence[object], page_size: int) -> "CacheLayout":
         for ci, s in enumerate(specs):
-            if s is not None and not isinstance(s, (PagedKVSpec, StateSpec)):
+            if s is not None and not isinstance(s, (PagedKVSpec, StateSpec, PagedStateSpec)):
                 raise CacheError(f"cache entry {ci}: unknown cache spec {s!r}")
         probe = core.Handle("allocator", core.call("global", None, "new_allocator", specs=[cache_spec_json(s) for s in specs],
                                                    pages=1, page_size=page_size, max_requests=1)["handle"])

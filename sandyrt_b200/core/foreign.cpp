@@ -61,6 +61,13 @@ public:
                         dt = n == "bfloat16" ? DType::BF16 : (n == "int32" ? DType::I32 : DType::F32);
                     }
                     info_.cache = CacheSpec::state(shape, dt);
+                } else if (kind == "paged_state") {
+                    std::vector<int64_t> shape;
+                    for (const Json& d : c->at("shape").items()) shape.push_back(d.as_int());
+                    int window = 0;
+                    if (const Json* w = c->find("window"))
+                        if (!w->is_null()) window = (int)w->as_int();
+                    info_.cache = CacheSpec::paged_with_state((int)c->at("n_kv_heads").as_int(), (int)c->at("head_dim").as_int(), window, shape);
                 }
             }
     }

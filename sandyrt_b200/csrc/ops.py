@@ -186,7 +186,7 @@ def kv_append(k_src, v_src, k_cache, v_cache, block_table, token_seq, positions)
     _check(code, "kv_append")
 
 
-def paged_attention(q, k_cache, v_cache, block_table, token_seq, positions, out, *,
+def paged_attention(q, k_cache, v_cache, block_table, token_seq, positions, out, *, sink=None, out_gate=None,
                     n_heads: int, scale: float, window: int = 0) -> None:
     """Causal attention of every token of the step over its request's pages (general kernel)."""
     _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out)
@@ -201,13 +201,13 @@ def paged_attention(q, k_cache, v_cache, block_table, token_seq, positions, out,
         raise KernelError("attention: q and out must be [T, H*D] of the cache's dtype")
     _i32(block_table, "block_table"); _i32(token_seq, "token_seq"); _i32(positions, "positions")
     lib = load_library("attention")
-    code = lib.sandy_paged_attention(_p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache),
+    code = lib.sandy_paged_attention_ext(_p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache),
                                      ctypes.c_longlong(page_stride), _p(block_table),
                                      ctypes.c_int(block_table.shape[1]), _p(token_seq), _p(positions), _p(out),
                                      ctypes.c_int(out.stride(0)), ctypes.c_int(T), ctypes.c_int(n_heads),
                                      ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(ps), ctypes.c_float(scale),
                                      ctypes.c_int(window), ctypes.c_int(num_pages), ctypes.c_int(_dt(q)),
-                                     _p(kernel_status(q.device)), _stream())
+                                     _p(sink), _p(out_gate), _p(kernel_status(q.device)), _stream())
     _check(code, f"paged_attention(H={n_heads},Hkv={hkv},D={d})")
 
 
@@ -228,7 +228,7 @@ CLUSTER_MAX_SPLITS = 8
 
 def decode_attention(q, k_cache, v_cache, block_table, token_seq, positions, out, *, n_heads: int,
                      scale: float, window: int = 0, num_splits: int = 1, scratch=None, cluster: bool = False,
-                     bulk: bool = False, mma: bool = False) -> None:
+                     bulk: bool = False, mma: bool = False, sink=None, out_gate=None) -> None:
     """Split-KV attention of single tokens (head sizes 16/32/64/128, 256 in bfloat16).  With
     `cluster` (2..8 splits) the splits merge through distributed shared memory inside one
     kernel; otherwise they go through `scratch` and a merge kernel.  `bulk` (at most 8 splits)
@@ -252,36 +252,36 @@ def decode_attention(q, k_cache, v_cache, block_table, token_seq, positions, out
         if num_splits > CLUSTER_MAX_SPLITS:
             raise UnsupportedShape(f"decode_attention: a cluster holds at most {CLUSTER_MAX_SPLITS} splits")
         lib = load_library("attention_decode_mma")
-        code = lib.sandy_decode_attention_mma(
+        code = lib.sandy_decode_attention_mma_ext(
             _p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache), ctypes.c_longlong(page_stride),
             _p(block_table), ctypes.c_int(block_table.shape[1]), _p(token_seq), _p(positions), _p(out),
             ctypes.c_int(out.stride(0)), ctypes.c_int(T), ctypes.c_int(n_heads), ctypes.c_int(hkv), ctypes.c_int(d),
             ctypes.c_int(ps), ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(num_splits),
-            ctypes.c_int(num_pages), ctypes.c_int(block_table.shape[1] * ps), _p(kernel_status(q.device)), _stream())
+            ctypes.c_int(num_pages), ctypes.c_int(block_table.shape[1] * ps), _p(sink), _p(out_gate), _p(kernel_status(q.device)), _stream())
         _check(code, f"decode_attention_mma(H={n_heads},Hkv={hkv},page={ps},splits={num_splits})")
         return
     if bulk:
         if num_splits > CLUSTER_MAX_SPLITS:
             raise UnsupportedShape(f"decode_attention: a cluster holds at most {CLUSTER_MAX_SPLITS} splits")
         lib = load_library("attention_decode_bulk")
-        code = lib.sandy_decode_attention_bulk(
+        code = lib.sandy_decode_attention_bulk_ext(
             _p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache), ctypes.c_longlong(page_stride),
             _p(block_table), ctypes.c_int(block_table.shape[1]), _p(token_seq), _p(positions), _p(out),
             ctypes.c_int(out.stride(0)), ctypes.c_int(T), ctypes.c_int(n_heads), ctypes.c_int(hkv), ctypes.c_int(d),
             ctypes.c_int(ps), ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(num_splits),
-            ctypes.c_int(num_pages), ctypes.c_int(_dt(q)), _p(kernel_status(q.device)), _stream())
+            ctypes.c_int(num_pages), ctypes.c_int(_dt(q)), _p(sink), _p(out_gate), _p(kernel_status(q.device)), _stream())
         _check(code, f"decode_attention_bulk(H={n_heads},Hkv={hkv},D={d},page={ps},splits={num_splits})")
         return
     if cluster and num_splits > 1:
         if num_splits > CLUSTER_MAX_SPLITS:
             raise UnsupportedShape(f"decode_attention: a cluster holds at most {CLUSTER_MAX_SPLITS} splits")
         lib = load_library("attention_decode")
-        code = lib.sandy_decode_attention_cluster(
+        code = lib.sandy_decode_attention_cluster_ext(
             _p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache), ctypes.c_longlong(page_stride),
             _p(block_table), ctypes.c_int(block_table.shape[1]), _p(token_seq), _p(positions), _p(out),
             ctypes.c_int(out.stride(0)), ctypes.c_int(T), ctypes.c_int(n_heads), ctypes.c_int(hkv), ctypes.c_int(d),
             ctypes.c_int(ps), ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(num_splits),
-            ctypes.c_int(num_pages), ctypes.c_int(_dt(q)), _p(kernel_status(q.device)), _stream())
+            ctypes.c_int(num_pages), ctypes.c_int(_dt(q)), _p(sink), _p(out_gate), _p(kernel_status(q.device)), _stream())
         _check(code, f"decode_attention_cluster(H={n_heads},Hkv={hkv},D={d},splits={num_splits})")
         return
     need = T * n_heads * num_splits * (d + 2) if num_splits > 1 else 0
@@ -289,26 +289,26 @@ def decode_attention(q, k_cache, v_cache, block_table, token_seq, positions, out
                  or not scratch.is_contiguous()):
         raise KernelError(f"decode_attention: {num_splits} splits need a float32 scratch of {need} elements")
     lib = load_library("attention_decode")
-    code = lib.sandy_decode_attention(_p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache),
+    code = lib.sandy_decode_attention_ext(_p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache),
                                       ctypes.c_longlong(page_stride), _p(block_table),
                                       ctypes.c_int(block_table.shape[1]), _p(token_seq), _p(positions), _p(out),
                                       ctypes.c_int(out.stride(0)), _p(scratch), ctypes.c_int(T), ctypes.c_int(n_heads),
                                       ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(ps), ctypes.c_float(scale),
                                       ctypes.c_int(window), ctypes.c_int(num_splits), ctypes.c_int(num_pages),
-                                      ctypes.c_int(_dt(q)), _p(kernel_status(q.device)), _stream())
+                                      ctypes.c_int(_dt(q)), _p(sink), _p(out_gate), _p(kernel_status(q.device)), _stream())
     _check(code, f"decode_attention(H={n_heads},Hkv={hkv},D={d},splits={num_splits})")
     if num_splits > 1:
         global LAUNCHES
         LAUNCHES += 1
 
 
-def prefill_attention(q, k_cache, v_cache, block_table, q_start, kv_before, out, *, n_heads: int,
+def prefill_attention(q, k_cache, v_cache, block_table, q_start, kv_before, out, *, sink=None, out_gate=None, n_heads: int,
                       max_q_len: int, scale: float, window: int = 0, tc=None) -> None:
     """Tensor-core attention of prompt portions (bfloat16, head sizes 16..128 in steps of 16).
     q_start: int32 [S+1] first new token of each request; kv_before: int32 [S].
     tc: True asks for the tcgen05 kernel (heads of 64), False for the mma.sync kernel, None
     picks the tcgen05 kernel where it takes the shape."""
-    _cuda(q, k_cache, v_cache, block_table, q_start, kv_before, out)
+    _cuda(q, k_cache, v_cache, block_table, q_start, kv_before, out, sink, out_gate)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     if q.dtype != torch.bfloat16 or d % 16 != 0 or d > 128:
         raise UnsupportedShape(f"prefill_attention: bfloat16 and head sizes 16..128 only, got {q.dtype}, {d}")
@@ -325,21 +325,71 @@ def prefill_attention(q, k_cache, v_cache, block_table, q_start, kv_before, out,
             _p(block_table), ctypes.c_int(block_table.shape[1]), _p(q_start), _p(kv_before), _p(out),
             ctypes.c_int(out.stride(0)), ctypes.c_int(S), ctypes.c_int(max_q_len), ctypes.c_int(n_heads),
             ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(ps), ctypes.c_float(scale), ctypes.c_int(window),
-            ctypes.c_int(num_pages), _p(kernel_status(q.device)), _stream())
+            ctypes.c_int(num_pages), _p(sink), _p(out_gate), _p(kernel_status(q.device)), _stream())
     if tc or (tc is None and d == 64):
-        code = load_library("attention_prefill_tc").sandy_prefill_attention_tc(*args)
+        code = load_library("attention_prefill_tc").sandy_prefill_attention_tc_ext(*args)
         if code != -1 or tc:
             _check(code, f"prefill_attention_tc(H={n_heads},Hkv={hkv},D={d})")
             return
     lib = load_library("attention_prefill")
-    code = lib.sandy_prefill_attention(_p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache),
+    code = lib.sandy_prefill_attention_ext(_p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache),
                                        ctypes.c_longlong(page_stride), _p(block_table),
                                        ctypes.c_int(block_table.shape[1]), _p(q_start), _p(kv_before), _p(out),
                                        ctypes.c_int(out.stride(0)), ctypes.c_int(S), ctypes.c_int(max_q_len),
                                        ctypes.c_int(n_heads), ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(ps),
                                        ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(num_pages),
-                                       _p(kernel_status(q.device)), _stream())
+                                       _p(sink), _p(out_gate), _p(kernel_status(q.device)), _stream())
     _check(code, f"prefill_attention(H={n_heads},Hkv={hkv},D={d})")
+
+
+def _f32(t, name: str) -> None:
+    if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+        raise KernelError(f"{name} must be a contiguous float32 tensor")
+
+
+def rmsnorm(x, gain, eps: float, out, rows=None) -> None:
+    """out[r] = x[rows[r] or r] / sqrt(mean(x^2) + eps) * gain; x float32 [*, width], gain float32 [width] or None."""
+    _cuda(x, gain, out, rows)
+    _f32(x, "x"); _f32(gain, "gain")
+    n_rows = out.shape[0]
+    code = load_library("rmsnorm").sandy_rmsnorm(_p(x), ctypes.c_int(x.stride(0)), _p(gain), _p(out), ctypes.c_int(out.stride(0)),
+                                                 _p(rows), ctypes.c_int(n_rows), ctypes.c_int(x.shape[1]), ctypes.c_float(eps),
+                                                 ctypes.c_int(_dt(out)), _stream())
+    _check(code, f"rmsnorm(width={x.shape[1]})")
+
+
+def rmsnorm_add(y, gain, eps: float, mult: float, x) -> None:
+    """x += mult * y / sqrt(mean(y^2) + eps) * gain, both float32."""
+    _cuda(x, gain, y)
+    _f32(x, "x"); _f32(y, "y"); _f32(gain, "gain")
+    code = load_library("rmsnorm").sandy_rmsnorm_add(_p(y), ctypes.c_int(y.stride(0)), _p(gain), _p(x), ctypes.c_int(x.stride(0)),
+                                                     ctypes.c_int(x.shape[0]), ctypes.c_int(x.shape[1]), ctypes.c_float(eps),
+                                                     ctypes.c_float(mult), _stream())
+    _check(code, f"rmsnorm_add(width={x.shape[1]})")
+
+
+def head_norm_gate(o, gain, gate, out, *, n_heads: int, eps: float, act: str = "sigmoid", scale: float = 1.0) -> None:
+    """Per (token, head): out = o / rms(o over the head) * gain * act(gate) * scale.  o float32 [T, H * dim]; gain
+    float32 [dim] (shared) or [H * dim]; gate [T, H * dim] or None; act "sigmoid" | "silu"."""
+    _cuda(o, gain, gate, out)
+    _f32(o, "o"); _f32(gain, "gain")
+    dim = o.shape[1] // n_heads
+    stride = dim if (gain is not None and gain.numel() == o.shape[1] and n_heads > 1) else 0
+    code = load_library("rmsnorm").sandy_head_norm_gate(
+        _p(o), ctypes.c_int(o.stride(0)), _p(gain), ctypes.c_int(stride), _p(gate), ctypes.c_int(0 if gate is None else gate.stride(0)),
+        ctypes.c_int(_dt(out) if gate is None else _dt(gate)), _p(out), ctypes.c_int(out.stride(0)), ctypes.c_int(_dt(out)),
+        ctypes.c_int(o.shape[0]), ctypes.c_int(n_heads), ctypes.c_int(dim), ctypes.c_float(eps),
+        ctypes.c_int({"sigmoid": 0, "silu": 1}[act]), ctypes.c_float(scale), _stream())
+    _check(code, f"head_norm_gate(H={n_heads},dim={dim})")
+
+
+def glu(a, b, out, act: str = "silu") -> None:
+    """out = act(a) * b; act "silu" | "gelu_tanh"."""
+    _cuda(a, b, out)
+    code = load_library("elementwise").sandy_glu(_p(a), _p(b), ctypes.c_int(a.stride(0)), _p(out), ctypes.c_int(out.stride(0)),
+                                                 ctypes.c_int(a.shape[0]), ctypes.c_int(a.shape[1]),
+                                                 ctypes.c_int({"silu": 0, "gelu_tanh": 1}[act]), ctypes.c_int(_dt(a)), _stream())
+    _check(code, "glu")
 
 
 def sample(logits, out_tokens, *, temperature=None, top_k=None, top_p=None, uniform=None, status=None,

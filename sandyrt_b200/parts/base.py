@@ -10,7 +10,7 @@ stream, with device memory wrapped as torch tensors.
 
 What each family must provide:
 
-  Mixer             cache_spec() -> PagedKVSpec | StateSpec | None
+  Mixer             cache_spec() -> PagedKVSpec | StateSpec | PagedStateSpec | None
                     forward(ctx, h, x, call) -> None      (x += mix(h), in place)
   FeedForward       forward(ctx, h, x) -> None            (x += ff(h), in place)
   Norm              forward(ctx, x, out, rows=None) -> None
@@ -57,6 +57,20 @@ class StateSpec:
     def to_json(self) -> Dict[str, Any]:
         return {"kind": "state", "shape": list(self.shape),
                 "dtype": {torch.float32: "float32", torch.bfloat16: "bfloat16", torch.int32: "int32"}[self.dtype]}
+
+
+@dataclasses.dataclass(frozen=True)
+class PagedStateSpec:
+    """Pages and a fixed-size state together: a mixer that runs softmax attention beside a recurrence.  The
+    pages fall into a group with every entry of equal page needs; the state is the entry's own."""
+    n_kv_heads: int
+    head_dim: int
+    shape: Tuple[int, ...]
+    window: Optional[int] = None
+
+    def to_json(self) -> Dict[str, Any]:
+        return {"kind": "paged_state", "n_kv_heads": self.n_kv_heads, "head_dim": self.head_dim, "window": self.window or 0,
+                "shape": list(self.shape), "dtype": "float32"}
 
 
 def cache_spec_json(spec) -> Optional[Dict[str, Any]]:

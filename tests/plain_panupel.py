@@ -35,9 +35,22 @@ def log_sigmoid(z: torch.Tensor) -> torch.Tensor:
     return -softplus(-z)
 
 
-def linear(w: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+# With ROUND_PRODUCTS set, every matrix product rounds its input to bfloat16 values and, unless the caller keeps
+# the result in 32-bit, its output too: what an engine that multiplies in bfloat16 with 32-bit sums does.  The
+# tests use this to learn how far rounding alone moves the logits of a given model.
+ROUND_PRODUCTS = False
+
+
+def _bf16(x: torch.Tensor) -> torch.Tensor:
+    return x.to(torch.bfloat16).to(x.dtype)
+
+
+def linear(w: torch.Tensor, h: torch.Tensor, keep32: bool = False) -> torch.Tensor:
     """Weights are stored [out, in]; rows of h are tokens."""
-    return h @ w.to(h.dtype).t()
+    if not ROUND_PRODUCTS:
+        return h @ w.to(h.dtype).t()
+    y = _bf16(h) @ w.to(h.dtype).t()
+    return y if keep32 else _bf16(y)
 
 
 # ---- rotary positions ------------------------------------------------------------------------------
@@ -106,9 +119,9 @@ def left_mixer(c: dict, w: Weights, pre: str, h: torch.Tensor, positions: torch.
         freqs = rotary_frequencies(rot["dims"], rot["base"], rot.get("scaling"))
         q, k = rotate(q, positions, freqs, rot["dims"]), rotate(k, positions, freqs, rot["dims"])
     o = sink_attention(q, k, v, float(c["scale"]), w.get(pre + "sink"))
-    gate = torch.sigmoid(linear(w[pre + "g"], h))                        # [T, H]
+    gate = torch.sigmoid(linear(w[pre + "g"], h, keep32=True))           # [T, H]
     o = o * gate[:, :, None]
-    return linear(w[pre + "o"], o.reshape(T, H * e))
+    return linear(w[pre + "o"], o.reshape(T, H * e), keep32=True)
 
 
 # ---- matrix memory (mLSTM) -------------------------------------------------------------------------
@@ -140,12 +153,12 @@ def right_mixer(c: dict, w: Weights, pre: str, h: torch.Tensor, eps: float) -> t
     q = (linear(w[pre + "q"], h) * d ** -0.5).view(T, H, d)
     k = linear(w[pre + "k"], h).view(T, H, d)
     v = linear(w[pre + "v"], h).view(T, H, e)
-    log_i = cap * torch.tanh((linear(w[pre + "i"], h) + w[pre + "i.b"].to(h.dtype)) / cap)
-    log_f = log_sigmoid(cap * torch.tanh((linear(w[pre + "f"], h) + w[pre + "f.b"].to(h.dtype)) / cap))
+    log_i = cap * torch.tanh((linear(w[pre + "i"], h, keep32=True) + w[pre + "i.b"].to(h.dtype)) / cap)
+    log_f = log_sigmoid(cap * torch.tanh((linear(w[pre + "f"], h, keep32=True) + w[pre + "f.b"].to(h.dtype)) / cap))
     o = torch.stack([matrix_memory(q[:, j], k[:, j], v[:, j], log_i[:, j], log_f[:, j])[0] for j in range(H)], dim=1)
     o = rms_norm(o, None, eps).reshape(T, H * e) * w[pre + "norm"].to(h.dtype)
     o = o * torch.sigmoid(linear(w[pre + "g"], h))
-    return linear(w[pre + "o"], o)
+    return linear(w[pre + "o"], o, keep32=True)
 
 
 def parallel_mixer(c: dict, w: Weights, pre: str, h, positions, eps):
@@ -192,19 +205,19 @@ def delta_mixer(c: dict, w: Weights, pre: str, h: torch.Tensor, eps: float) -> t
     k = silu(short_conv(linear(w[pre + "k"], h), w[pre + "k.conv"])).view(T, G, d)
     v = silu(short_conv(linear(w[pre + "v"], h), w[pre + "v.conv"])).view(T, H, e)
     q, k = unit(q) * d ** -0.5, unit(k)
-    beta = torch.sigmoid(linear(w[pre + "b"], h))                                         # [T, H]
+    beta = torch.sigmoid(linear(w[pre + "b"], h, keep32=True))                                         # [T, H]
     decay = torch.exp(-torch.exp(w[pre + "A_log"].to(h.dtype)) *
-                      softplus(linear(w[pre + "a"], h) + w[pre + "dt_bias"].to(h.dtype)))  # [T, H]
+                      softplus(linear(w[pre + "a"], h, keep32=True) + w[pre + "dt_bias"].to(h.dtype)))  # [T, H]
     o = torch.stack([delta_rule(q[:, j // (H // G)], k[:, j // (H // G)], v[:, j], beta[:, j], decay[:, j])[0]
                      for j in range(H)], dim=1)                                           # [T, H, e]
     o = rms_norm(o, w[pre + "norm"].to(h.dtype), eps)
     o = o.reshape(T, H * e) * silu(linear(w[pre + "g"], h))
-    return linear(w[pre + "o"], o)
+    return linear(w[pre + "o"], o, keep32=True)
 
 
 # ---- feed-forward, layer, model --------------------------------------------------------------------
 def gated_mlp(w: Weights, pre: str, h: torch.Tensor) -> torch.Tensor:
-    return linear(w[pre + "down"], silu(linear(w[pre + "gate"], h)) * linear(w[pre + "up"], h))
+    return linear(w[pre + "down"], silu(linear(w[pre + "gate"], h)) * linear(w[pre + "up"], h), keep32=True)
 
 
 def layer(config: dict, w: Weights, i: int, x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
@@ -238,6 +251,17 @@ def run_order(config: dict) -> List[Tuple[int, bool]]:
     return order + [(i, False) for i in range(stop, n)]
 
 
+def forward_rounded(config: dict, w: Weights, tokens: List[int], dtype=torch.float64):
+    """`forward` with every product's operands (and results, where an engine keeps them in 16 bits) rounded to
+    bfloat16 values."""
+    global ROUND_PRODUCTS
+    ROUND_PRODUCTS = True
+    try:
+        return forward(config, w, tokens, dtype)
+    finally:
+        ROUND_PRODUCTS = False
+
+
 def forward(config: dict, w: Weights, tokens: List[int], dtype=torch.float64):
     """Logits [T, vocab] and the residual stream after every layer run [runs, T, width]."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in w.items()}
@@ -247,8 +271,8 @@ def forward(config: dict, w: Weights, tokens: List[int], dtype=torch.float64):
     streams = []
     for i, mix_in in run_order(config):
         if mix_in:
-            x = linear(w["loop.in"], torch.cat([x, x0], dim=-1))
+            x = linear(w["loop.in"], torch.cat([x, x0], dim=-1), keep32=True)
         x = layer(config, w, i, x, positions)
         streams.append(x)
     y = rms_norm(x, w["final.norm"], float(config["norm"]["eps"]))
-    return linear(w["head"], y), torch.stack(streams)
+    return linear(w["head"], y, keep32=True), torch.stack(streams)
