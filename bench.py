@@ -458,7 +458,8 @@ def hybrid(dtype_name: str, layers: int, batch: int, steps: int, warmup: int) ->
             cfg.validate()
             model = build_model(cfg)
             model.bind_random(0, getattr(torch, dtype_name))
-            llm = LLM(model, cache_tokens=16 * 1024 + 4096, max_live=16, max_step_tokens=4096, prefill_chunk_tokens=2048)
+            llm = LLM(model, cache_tokens=16 * 1024 + 4096, max_live=16, max_step_tokens=4096, prefill_chunk_tokens=2048,
+                      max_context_tokens=1024)       # GPT-2's own limit, for both
             vocab = cfg.vocab_size
             row = {"weight_bytes": model.weight_bytes()}
             for b in (1, batch):

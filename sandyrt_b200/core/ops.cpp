@@ -670,29 +670,45 @@ void conv_tail(const Launch& l, const StepSeqs& s, const DeltaShape& d, const Te
 }
 
 void delta_scan(const Launch& l, const StepSeqs& s, const DeltaShape& d, const Tensor& qkv, const Tensor& bg, const StateView& state,
-                Tensor& out) {
+                Tensor& out, int max_q_len) {
     if (out.dtype != DType::F32 || out.cols != (int64_t)d.n_heads * d.v_dim || qkv.dtype != DType::F32)
         throw KernelError("delta_scan: float32 qkv and out [T, H * e] expected");
     static auto fn = SANDY_KERNEL(matrix_state, sandy_delta_scan);
+    static auto chunked = SANDY_KERNEL(matrix_state, sandy_delta_chunk_scan);
+    const int long_from = max_q_len >= kChunkedFrom ? kChunkedFrom : 0;
     const double st = 2.0 * s.n_seqs * d.n_heads * d.qk_dim * d.v_dim * 4.0;
     OpTimer timer(l, "delta rule: recurrence", st + tensor_bytes(&qkv) + tensor_bytes(&out), 6.0 * s.n_tokens * d.n_heads * d.qk_dim * d.v_dim);
+    const std::string shape = "(d=" + std::to_string(d.qk_dim) + ",e=" + std::to_string(d.v_dim) + ")";
     check(fn((const float*)qkv.data, (int)qkv.ld, (const float*)bg.data, (float*)state.data, state.row_elems, s.q_start, s.seq_slots,
-             (float*)out.data, (int)out.ld, s.n_seqs, d.n_heads, d.n_qk_heads, d.qk_dim, d.v_dim, l.stream),
-          "delta_scan(d=" + std::to_string(d.qk_dim) + ",e=" + std::to_string(d.v_dim) + ")");
+             (float*)out.data, (int)out.ld, s.n_seqs, d.n_heads, d.n_qk_heads, d.qk_dim, d.v_dim, long_from, l.stream),
+          "delta_scan" + shape);
+    if (long_from)
+        check(chunked((const float*)qkv.data, (int)qkv.ld, (const float*)bg.data, (float*)state.data, state.row_elems, s.q_start,
+                      s.seq_slots, (float*)out.data, (int)out.ld, s.n_seqs, d.n_heads, d.n_qk_heads, d.qk_dim, d.v_dim, long_from,
+                      l.stream),
+              "delta_chunk_scan" + shape);
 }
 
 void mlstm_scan(const Launch& l, const StepSeqs& s, const MlstmShape& m, const Tensor& proj, const Tensor& gates,
-                const float* gate_bias, const StateView& state, Tensor& out) {
+                const float* gate_bias, const StateView& state, Tensor& out, int max_q_len) {
     if (out.dtype != DType::F32 || out.cols != (int64_t)m.n_heads * m.v_dim || gates.dtype != DType::F32 || gates.cols < 2 * m.n_heads ||
         state.dtype != DType::F32 || state.row_elems < mlstm_state_floats(m.n_heads, m.qk_dim, m.v_dim))
         throw KernelError("mlstm_scan: shapes disagree");
     static auto fn = SANDY_KERNEL(matrix_state, sandy_mlstm_scan);
+    static auto chunked = SANDY_KERNEL(matrix_state, sandy_mlstm_chunk_scan);
+    const int long_from = max_q_len >= kChunkedFrom ? kChunkedFrom : 0;
     const double st = 2.0 * s.n_seqs * m.n_heads * m.qk_dim * m.v_dim * 4.0;
     OpTimer timer(l, "matrix memory: recurrence", st + tensor_bytes(&out), 4.0 * s.n_tokens * m.n_heads * m.qk_dim * m.v_dim);
+    const std::string shape = "(d=" + std::to_string(m.qk_dim) + ",e=" + std::to_string(m.v_dim) + ")";
     check(fn(proj.data, (int)proj.ld, code_of(proj.dtype), m.q_off, m.k_off, m.v_off, (const float*)gates.data, (int)gates.ld, gate_bias,
              m.cap, m.q_scale, (float*)state.data, state.row_elems, s.q_start, s.seq_slots, (float*)out.data, (int)out.ld, s.n_seqs,
-             m.n_heads, m.qk_dim, m.v_dim, l.stream),
-          "mlstm_scan(d=" + std::to_string(m.qk_dim) + ",e=" + std::to_string(m.v_dim) + ")");
+             m.n_heads, m.qk_dim, m.v_dim, long_from, l.stream),
+          "mlstm_scan" + shape);
+    if (long_from)
+        check(chunked(proj.data, (int)proj.ld, code_of(proj.dtype), m.q_off, m.k_off, m.v_off, (const float*)gates.data, (int)gates.ld,
+                      gate_bias, m.cap, m.q_scale, (float*)state.data, state.row_elems, s.q_start, s.seq_slots, (float*)out.data,
+                      (int)out.ld, s.n_seqs, m.n_heads, m.qk_dim, m.v_dim, long_from, l.stream),
+              "mlstm_chunk_scan" + shape);
 }
 
 void sample(const Launch& l, const Tensor& logits, int* out_tokens, const float* temperature, const int* top_k,

@@ -185,18 +185,25 @@ struct StepSeqs {                                                  // the step's
 };
 struct DeltaShape { int n_heads = 0, n_qk_heads = 0, qk_dim = 0, v_dim = 0, n_taps = 0; };
 // conv + silu + unit vectors + gates.  proj [T, >= channels] (q, k, v channels first); taps float32 [channels, n_taps];
-// gates float32 [T, 2H] (beta's pre-activation, then the decay's); qkv float32 [T, channels]; bg float32 [T, 2H].
+// gates float32 [T, 2H] (beta's pre-activation, then the decay's); qkv float32 [T, channels]; bg float32 [T, 2H]
+// (beta, then the logarithm of the decay).
 void delta_prepare(const Launch& l, const StepSeqs& s, const DeltaShape& d, const Tensor& proj, const Tensor& taps,
                    const Tensor& gates, const float* a_log, const float* dt_bias, const StateView& state, int64_t tail_off,
                    float q_scale, Tensor& qkv, Tensor& bg);
 void conv_tail(const Launch& l, const StepSeqs& s, const DeltaShape& d, const Tensor& proj, const StateView& state,
                int64_t tail_off);
+// From how many tokens of one request on a step's recurrence runs a chunk of tokens at a time (parallel inside the
+// chunk) instead of token by token.  Token by token costs about 0.8 us a token and head (a dependent chain of some 240
+// instructions), a chunk of 32 about 2 us, so the chunked kernel is ahead from a handful of tokens on.
+constexpr int kChunkedFrom = 8;
+// `max_q_len`: the step's longest portion.  Below kChunkedFrom only the token-by-token kernel is launched; from there
+// on both are, each taking the requests of its own kind (which requests those are is read on the device).
 void delta_scan(const Launch& l, const StepSeqs& s, const DeltaShape& d, const Tensor& qkv, const Tensor& bg,
-                const StateView& state, Tensor& out);
+                const StateView& state, Tensor& out, int max_q_len);
 struct MlstmShape { int n_heads = 0, qk_dim = 0, v_dim = 0, q_off = 0, k_off = 0, v_off = 0; float cap = 1.0f, q_scale = 1.0f; };
 // gates float32 [T, >= 2H]: input-gate pre-activations, then forget-gate ones; gate_bias float32 [2H].
 void mlstm_scan(const Launch& l, const StepSeqs& s, const MlstmShape& m, const Tensor& proj, const Tensor& gates,
-                const float* gate_bias, const StateView& state, Tensor& out);
+                const float* gate_bias, const StateView& state, Tensor& out, int max_q_len);
 
 // Choose one token per row of float32 `logits`; per-row option arrays may be null.  With `feedback`
 // the drawn token also replaces the row's input token, its position moves on, and the token is

@@ -374,7 +374,7 @@ public:
         ms.q_scale = 1.0f / std::sqrt((float)dr_);
         Tensor read = ws.get("mix_read", T, (int64_t)Hr_ * er_, DType::F32);
         Tensor gate_cols = gates.col_range(H_, H_ + 2 * Hr_);
-        ops::mlstm_scan(l, seqs, ms, wide, gate_cols, (const float*)gate_bias_.view.data, state, read);
+        ops::mlstm_scan(l, seqs, ms, wide, gate_cols, (const float*)gate_bias_.view.data, state, read, ctx.max_q_len);
         Tensor o_right = heads.col_range(k_left, k_left + (int64_t)Hr_ * er_);
         Tensor out_gate = wide.col_range(ms.v_off + Hr_ * er_, ms.v_off + 2 * Hr_ * er_);
         ops::head_norm_gate(l, read, &right_gain_.view, &out_gate, ops::GateAct::Sigmoid, right_scale_, eps_, Hr_, o_right);
@@ -472,7 +472,7 @@ public:
                            state, tail_off, 1.0f / std::sqrt((float)d_), qkv, bg);
         ops::conv_tail(l, seqs, ds, wide, state, tail_off);
         Tensor read = ws.get("mix_read", T, (int64_t)H_ * e_, DType::F32);
-        ops::delta_scan(l, seqs, ds, qkv, bg, state, read);
+        ops::delta_scan(l, seqs, ds, qkv, bg, state, read, ctx.max_q_len);
         Tensor normed = ws.get("delta_normed", T, (int64_t)H_ * e_, ctx.compute_dtype);
         Tensor out_gate = wide.col_range(channels_, n_wide_);
         ops::head_norm_gate(l, read, &gain_.view, &out_gate, ops::GateAct::Silu, 1.0f, eps_, H_, normed);

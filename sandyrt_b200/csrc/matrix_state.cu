@@ -84,7 +84,7 @@ delta_prepare_kernel(const T* __restrict__ proj, int ld, const float* __restrict
     for (int h = threadIdx.x; h < n_heads; h += blockDim.x) {
         const float b = gates[(size_t)t * ld_gates + h], a = gates[(size_t)t * ld_gates + n_heads + h];
         bg[(size_t)t * 2 * n_heads + h] = 1.0f / (1.0f + expf(-b));
-        bg[(size_t)t * 2 * n_heads + n_heads + h] = expf(-expf(a_log[h]) * softplus_f(a + dt_bias[h]));
+        bg[(size_t)t * 2 * n_heads + n_heads + h] = -expf(a_log[h]) * softplus_f(a + dt_bias[h]);      // log of the decay
     }
 }
 
@@ -130,18 +130,21 @@ __device__ __forceinline__ void warp_sum_all(float (&v)[N]) {
 __device__ __forceinline__ int per_token(int d) { return 2 * d + COLS + 2; }
 
 // ---- gated delta rule: the recurrence ---------------------------------------------------------------------
-// qkv: float32 [T, ld] rows of (q [Hqk * d], k [Hqk * d], v [H * e]) as delta_prepare left them; bg: [T, 2H].
+// qkv: float32 [T, ld] rows of (q [Hqk * d], k [Hqk * d], v [H * e]) as delta_prepare left them; bg: [T, 2H]
+// (beta, then the logarithm of the decay).  Requests that bring `long_from` tokens or more are left to the chunked
+// kernel below (0: none are).
 template <int R>
 __global__ void __launch_bounds__(THREADS)
 delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ bg, float* __restrict__ state,
                   long long state_stride, const int* __restrict__ q_start, const int* __restrict__ seq_slots,
-                  float* __restrict__ out, int ld_out, int n_heads, int n_qk_heads, int d, int e) {
+                  float* __restrict__ out, int ld_out, int n_heads, int n_qk_heads, int d, int e, int long_from) {
     extern __shared__ float stage[];                  // [CHUNK][per_token]
     const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * COLS;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int qh = h / (n_heads / n_qk_heads);
     const int per = per_token(d);
     const int t0 = q_start[s], t1 = q_start[s + 1];
+    if (long_from > 0 && t1 - t0 >= long_from) return;
     float* S = state + (long long)seq_slots[s] * state_stride + (long long)h * e * d;    // [e][d]
     pdl_wait();
     float st[R][CPW];
@@ -170,7 +173,10 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict
                 else if (j < 2 * d + COLS) {
                     const int col = col0 + j - 2 * d;
                     v = col < e ? row[2 * n_qk_heads * d + h * e + col] : 0.0f;
-                } else v = bg[(size_t)(tc + tok) * 2 * n_heads + (j - 2 * d - COLS) * n_heads + h];
+                } else {
+                    v = bg[(size_t)(tc + tok) * 2 * n_heads + (j - 2 * d - COLS) * n_heads + h];
+                    if (j == 2 * d + COLS + 1) v = expf(v);       // bg holds the decay's logarithm
+                }
             }
             pre[x] = v;
         }
@@ -244,12 +250,13 @@ __global__ void __launch_bounds__(THREADS)
 mlstm_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ gates,
                   int ld_gates, const float* __restrict__ gate_bias, float cap, float q_scale, float* __restrict__ state,
                   long long state_stride, const int* __restrict__ q_start, const int* __restrict__ seq_slots,
-                  float* __restrict__ out, int ld_out, int n_heads, int d, int e) {
+                  float* __restrict__ out, int ld_out, int n_heads, int d, int e, int long_from) {
     extern __shared__ float stage[];
     const int s = blockIdx.x, h = blockIdx.y, z = blockIdx.z, col0 = z * COLS, Z = gridDim.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int per = per_token(d);
     const int t0 = q_start[s], t1 = q_start[s + 1];
+    if (long_from > 0 && t1 - t0 >= long_from) return;
     float* base = state + (long long)seq_slots[s] * state_stride;
     float* S = base + (long long)h * e * d;
     float* n_st = base + (long long)n_heads * e * d + ((long long)h * Z + z) * d;
@@ -354,6 +361,388 @@ mlstm_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int 
     }
 }
 
+// ---- the same recurrences, a chunk of tokens at a time ----------------------------------------------------
+// Walking a prompt token by token leaves a warp one short dependent chain per token (measured: 240 instructions
+// at 6 cycles each), so a request that brings many tokens is taken CC tokens at a time instead.  Inside a chunk
+// everything is a small matrix product in float32 (FFMA; the design wants the recurrences in 32-bit, so no tensor
+// cores), parallel over the chunk's tokens; only the state goes from chunk to chunk.  With S0 the state before the
+// chunk, tokens 1..CC, and sums over j <= t unless said otherwise:
+//
+//   matrix memory   F_t = sum_{l<=t} log f_l;  a_j = log i_j - F_j;  M_t = max(m0, max_{j<=t} a_j);  m_t = F_t + M_t
+//                   w(t, j) = exp(a_j - M_t) (never above one);  c_t = exp(m0 - M_t)
+//                   S_t = c_t S0 + sum_j w(t, j) k_j v_j^T;   n_t likewise
+//                   o_t = (c_t S0^T q_t + sum_j w(t, j) (q_t . k_j) v_j) / (max(|n_t . q_t|, exp(-m_t)) + 1e-6)
+//   delta rule      G_t = sum_{l<=t} log g_l;  r(t, j) = exp(G_t - G_j)
+//                   u_t = beta_t (v_t - exp(G_t) S0^T k_t - sum_{j<t} r(t, j) (k_t . k_j) u_j)      a triangular system,
+//                                                                                                   solved row by row
+//                   o_t = exp(G_t) S0^T q_t + sum_j r(t, j) (q_t . k_j) u_j
+//                   S_CC = exp(G_CC) S0 + sum_j r(CC, j) k_j u_j^T
+//
+// A block owns COLS columns of one head's state, as in the kernels above (and recomputes the products that do not
+// depend on the column: q . k, k . k).  Tokens beyond a request's last are given weights of zero (log i = -inf,
+// beta = 0) and decays of one, so that a partly filled chunk leaves the state where its last token left it.
+constexpr int CC = 32;                 // tokens per chunk
+constexpr int CT = 128;                // threads
+constexpr int LA = CC + 4;             // row pitch of the CC x CC matrices
+
+// X Y^T for a tile of 2 rows of X and 4 rows of Y, rows of `len` floats (a multiple of 4) at pitch ld.
+__device__ __forceinline__ void tile_2x4(const float* __restrict__ X, const float* __restrict__ Y, int ld, int len,
+                                         float (&acc)[2][4]) {
+#pragma unroll
+    for (int a = 0; a < 2; a++)
+#pragma unroll
+        for (int b = 0; b < 4; b++) acc[a][b] = 0.0f;
+    for (int i = 0; i < len; i += 4) {
+        float4 x[2], y[4];
+#pragma unroll
+        for (int a = 0; a < 2; a++) x[a] = *reinterpret_cast<const float4*>(X + a * ld + i);
+#pragma unroll
+        for (int b = 0; b < 4; b++) y[b] = *reinterpret_cast<const float4*>(Y + b * ld + i);
+#pragma unroll
+        for (int a = 0; a < 2; a++)
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+                acc[a][b] = fmaf(x[a].x, y[b].x, acc[a][b]);
+                acc[a][b] = fmaf(x[a].y, y[b].y, acc[a][b]);
+                acc[a][b] = fmaf(x[a].z, y[b].z, acc[a][b]);
+                acc[a][b] = fmaf(x[a].w, y[b].w, acc[a][b]);
+            }
+    }
+}
+
+struct ChunkSmem {
+    float *q, *k, *v, *qk, *kk, *s0, *n0, *v1, *v2, *v3, *v4;
+};
+__device__ __forceinline__ ChunkSmem carve(float* base, int dp, bool two) {
+    ChunkSmem m;
+    const int ld = dp + 4;
+    m.q = base;
+    m.k = m.q + CC * ld;
+    m.v = m.k + CC * ld;                 // [CC][COLS]
+    m.qk = m.v + CC * COLS;              // [CC][LA]
+    m.kk = m.qk + CC * LA;               // [CC][LA] (delta rule only)
+    m.s0 = m.kk + (two ? CC * LA : 0);   // [dp][COLS]
+    m.n0 = m.s0 + dp * COLS;             // [dp]
+    m.v1 = m.n0 + dp;                    // four vectors of CC
+    m.v2 = m.v1 + CC;
+    m.v3 = m.v2 + CC;
+    m.v4 = m.v3 + CC;
+    return m;
+}
+size_t chunk_smem_bytes(int d, bool two) {
+    const int dp = (d + 3) / 4 * 4;
+    return (size_t)(2 * CC * (dp + 4) + CC * COLS + (two ? 2 : 1) * CC * LA + dp * COLS + dp + 4 * CC) * sizeof(float);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(CT)
+mlstm_chunk_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ gates,
+                   int ld_gates, const float* __restrict__ gate_bias, float cap, float q_scale, float* __restrict__ state,
+                   long long state_stride, const int* __restrict__ q_start, const int* __restrict__ seq_slots,
+                   float* __restrict__ out, int ld_out, int n_heads, int d, int e, int long_from) {
+    extern __shared__ __align__(16) float chunk_raw[];
+    const int s = blockIdx.x, h = blockIdx.y, z = blockIdx.z, col0 = z * COLS, Z = gridDim.z;
+    const int t0 = q_start[s], t1 = q_start[s + 1];
+    if (t1 - t0 < long_from) return;
+    const int dp = (d + 3) / 4 * 4, ldq = dp + 4;
+    const ChunkSmem m = carve(chunk_raw, dp, false);
+    float* li = m.v1;     // a_j
+    float* Ms = m.v2;     // M_t
+    float* cw = m.v3;     // c_t
+    float* Fs = m.v4;     // F_t
+    __shared__ float m0_s;
+    const int tid = threadIdx.x;
+    float* base = state + (long long)seq_slots[s] * state_stride;
+    float* S = base + (long long)h * e * d;
+    float* n_st = base + (long long)n_heads * e * d + ((long long)h * Z + z) * d;
+    float* m_st = base + (long long)n_heads * e * d + (long long)n_heads * Z * d + (long long)h * Z + z;
+    const float bias_i = gate_bias[h], bias_f = gate_bias[n_heads + h];
+    pdl_wait();
+    for (int x = tid; x < dp * COLS; x += CT) {
+        const int c = x / dp, i = x % dp;                // consecutive threads read consecutive rows of a column
+        m.s0[i * COLS + c] = (i < d && col0 + c < e) ? S[(size_t)(col0 + c) * d + i] : 0.0f;
+    }
+    for (int i = tid; i < dp; i += CT) m.n0[i] = i < d ? n_st[i] : 0.0f;
+    if (tid == 0) m0_s = *m_st;
+    const int tr = tid / 8, tc4 = tid % 8;               // this thread's 2 x 4 tile of q k^T
+    const int ot = tid / 4, oc = (tid % 4) * 4;          // this thread's token and four columns of the read-out
+    for (int tc = t0; tc < t1; tc += CC) {
+        const int n_tok = min(CC, t1 - tc);
+        __syncthreads();
+        for (int x = tid; x < CC * dp; x += CT) {
+            const int t = x / dp, i = x % dp;
+            const bool live = t < n_tok && i < d;
+            const T* row = proj + (size_t)(tc + t) * ld;
+            m.q[t * ldq + i] = live ? to_f32(row[q_off + h * d + i]) * q_scale : 0.0f;
+            m.k[t * ldq + i] = live ? to_f32(row[k_off + h * d + i]) : 0.0f;
+        }
+        for (int x = tid; x < CC * COLS; x += CT) {
+            const int t = x / COLS, c = x % COLS;
+            m.v[x] = (t < n_tok && col0 + c < e) ? to_f32(proj[(size_t)(tc + t) * ld + v_off + h * e + col0 + c]) : 0.0f;
+        }
+        if (tid < CC) {
+            const bool live = tid < n_tok;
+            const float* g = gates + (size_t)(tc + tid) * ld_gates;
+            li[tid] = live ? cap * tanhf((g[h] + bias_i) / cap) : -INFINITY;
+            Fs[tid] = live ? log_sigmoid_f(cap * tanhf((g[n_heads + h] + bias_f) / cap)) : 0.0f;
+        }
+        __syncthreads();
+        if (tid == 0) {                                   // the running sums and maxima, one after the other
+            float F = 0.0f, M = m0_s;
+            for (int t = 0; t < CC; t++) {
+                F += Fs[t];
+                const float a = li[t] - F;
+                M = fmaxf(M, a);
+                li[t] = a;
+                Fs[t] = F;
+                Ms[t] = M;
+                cw[t] = expf(m0_s - M);
+            }
+        }
+        {
+            float acc[2][4];
+            tile_2x4(m.q + (2 * tr) * ldq, m.k + (4 * tc4) * ldq, ldq, dp, acc);
+#pragma unroll
+            for (int a = 0; a < 2; a++)
+#pragma unroll
+                for (int b = 0; b < 4; b++) m.qk[(2 * tr + a) * LA + 4 * tc4 + b] = acc[a][b];
+        }
+        __syncthreads();
+        for (int x = tid; x < CC * CC; x += CT) {         // weights: w(t, j) (q_t . k_j), zero above the diagonal
+            const int t = x / CC, j = x % CC;
+            m.qk[t * LA + j] = j <= t ? m.qk[t * LA + j] * expf(li[j] - Ms[t]) : 0.0f;
+        }
+        __syncthreads();
+        // read-out of token ot, columns oc .. oc + 3
+        float o[4] = {0.0f, 0.0f, 0.0f, 0.0f}, nq = 0.0f;
+        {
+            const float* qrow = m.q + ot * ldq;
+            for (int i = 0; i < dp; i++) {
+                const float qi = qrow[i];
+                const float4 sv = *reinterpret_cast<const float4*>(m.s0 + i * COLS + oc);
+                o[0] = fmaf(qi, sv.x, o[0]); o[1] = fmaf(qi, sv.y, o[1]); o[2] = fmaf(qi, sv.z, o[2]); o[3] = fmaf(qi, sv.w, o[3]);
+                nq = fmaf(qi, m.n0[i], nq);
+            }
+            const float c = cw[ot];
+            o[0] *= c; o[1] *= c; o[2] *= c; o[3] *= c; nq *= c;
+            const float* prow = m.qk + ot * LA;
+            for (int j = 0; j <= ot; j++) {
+                const float p = prow[j];
+                const float4 vv = *reinterpret_cast<const float4*>(m.v + j * COLS + oc);
+                o[0] = fmaf(p, vv.x, o[0]); o[1] = fmaf(p, vv.y, o[1]); o[2] = fmaf(p, vv.z, o[2]); o[3] = fmaf(p, vv.w, o[3]);
+                nq += p;
+            }
+            if (ot < n_tok) {
+                const float den = fmaxf(fabsf(nq), expf(-(Fs[ot] + Ms[ot]))) + 1e-6f;
+#pragma unroll
+                for (int c4 = 0; c4 < 4; c4++)
+                    if (col0 + oc + c4 < e) out[(size_t)(tc + ot) * ld_out + h * e + col0 + oc + c4] = o[c4] / den;
+            }
+        }
+        // the state after the chunk: rows i = ot, ot + 32, ..., columns oc .. oc + 3 (kept in registers until everyone has read S0)
+        constexpr int MAXR = 8;                           // rows of the state a thread owns: d <= 256
+        float sn[MAXR][4], nn[MAXR];
+        const float c_last = cw[CC - 1], M_last = Ms[CC - 1];
+#pragma unroll
+        for (int r = 0; r < MAXR; r++) {
+            const int i = ot + 32 * r;
+            if (i < dp) {
+                const float4 sv = *reinterpret_cast<const float4*>(m.s0 + i * COLS + oc);
+                sn[r][0] = c_last * sv.x; sn[r][1] = c_last * sv.y; sn[r][2] = c_last * sv.z; sn[r][3] = c_last * sv.w;
+                nn[r] = c_last * m.n0[i];
+            }
+        }
+        for (int j = 0; j < CC; j++) {
+            const float w = expf(li[j] - M_last);
+            const float4 vv = *reinterpret_cast<const float4*>(m.v + j * COLS + oc);
+#pragma unroll
+            for (int r = 0; r < MAXR; r++) {
+                const int i = ot + 32 * r;
+                if (i < dp) {
+                    const float wk = w * m.k[j * ldq + i];
+                    sn[r][0] = fmaf(wk, vv.x, sn[r][0]); sn[r][1] = fmaf(wk, vv.y, sn[r][1]);
+                    sn[r][2] = fmaf(wk, vv.z, sn[r][2]); sn[r][3] = fmaf(wk, vv.w, sn[r][3]);
+                    nn[r] += wk;
+                }
+            }
+        }
+        const float m_new = Fs[CC - 1] + M_last;
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < MAXR; r++) {
+            const int i = ot + 32 * r;
+            if (i < dp) {
+                *reinterpret_cast<float4*>(m.s0 + i * COLS + oc) = make_float4(sn[r][0], sn[r][1], sn[r][2], sn[r][3]);
+                if (oc == 0) m.n0[i] = nn[r];
+            }
+        }
+        if (tid == 0) m0_s = m_new;
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+    for (int x = tid; x < dp * COLS; x += CT) {
+        const int c = x / dp, i = x % dp;
+        if (i < d && col0 + c < e) S[(size_t)(col0 + c) * d + i] = m.s0[i * COLS + c];
+    }
+    for (int i = tid; i < d; i += CT) n_st[i] = m.n0[i];
+    if (tid == 0) *m_st = m0_s;
+}
+
+__global__ void __launch_bounds__(CT)
+delta_chunk_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ bg, float* __restrict__ state,
+                   long long state_stride, const int* __restrict__ q_start, const int* __restrict__ seq_slots,
+                   float* __restrict__ out, int ld_out, int n_heads, int n_qk_heads, int d, int e, int long_from) {
+    extern __shared__ __align__(16) float chunk_raw[];
+    const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * COLS;
+    const int t0 = q_start[s], t1 = q_start[s + 1];
+    if (t1 - t0 < long_from) return;
+    const int qh = h / (n_heads / n_qk_heads);
+    const int dp = (d + 3) / 4 * 4, ldq = dp + 4;
+    const ChunkSmem m = carve(chunk_raw, dp, true);
+    float* beta = m.v1;
+    float* G = m.v2;      // running sum of the decays' logarithms
+    const int tid = threadIdx.x;
+    float* S = state + (long long)seq_slots[s] * state_stride + (long long)h * e * d;
+    pdl_wait();
+    for (int x = tid; x < dp * COLS; x += CT) {
+        const int c = x / dp, i = x % dp;
+        m.s0[i * COLS + c] = (i < d && col0 + c < e) ? S[(size_t)(col0 + c) * d + i] : 0.0f;
+    }
+    const int tr = tid / 8, tc4 = tid % 8;
+    const int ot = tid / 4, oc = (tid % 4) * 4;
+    for (int tc = t0; tc < t1; tc += CC) {
+        const int n_tok = min(CC, t1 - tc);
+        __syncthreads();
+        for (int x = tid; x < CC * dp; x += CT) {
+            const int t = x / dp, i = x % dp;
+            const bool live = t < n_tok && i < d;
+            const float* row = qkv + (size_t)(tc + t) * ld;
+            m.q[t * ldq + i] = live ? row[qh * d + i] : 0.0f;
+            m.k[t * ldq + i] = live ? row[(n_qk_heads + qh) * d + i] : 0.0f;
+        }
+        for (int x = tid; x < CC * COLS; x += CT) {
+            const int t = x / COLS, c = x % COLS;
+            m.v[x] = (t < n_tok && col0 + c < e) ? qkv[(size_t)(tc + t) * ld + 2 * n_qk_heads * d + h * e + col0 + c] : 0.0f;
+        }
+        if (tid < CC) {
+            const bool live = tid < n_tok;
+            beta[tid] = live ? bg[(size_t)(tc + tid) * 2 * n_heads + h] : 0.0f;
+            G[tid] = live ? bg[(size_t)(tc + tid) * 2 * n_heads + n_heads + h] : 0.0f;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float acc = 0.0f;
+            for (int t = 0; t < CC; t++) {
+                acc += G[t];
+                G[t] = acc;
+            }
+        }
+        {
+            float acc[2][4];
+            tile_2x4(m.q + (2 * tr) * ldq, m.k + (4 * tc4) * ldq, ldq, dp, acc);
+#pragma unroll
+            for (int a = 0; a < 2; a++)
+#pragma unroll
+                for (int b = 0; b < 4; b++) m.qk[(2 * tr + a) * LA + 4 * tc4 + b] = acc[a][b];
+            tile_2x4(m.k + (2 * tr) * ldq, m.k + (4 * tc4) * ldq, ldq, dp, acc);
+#pragma unroll
+            for (int a = 0; a < 2; a++)
+#pragma unroll
+                for (int b = 0; b < 4; b++) m.kk[(2 * tr + a) * LA + 4 * tc4 + b] = acc[a][b];
+        }
+        __syncthreads();
+        for (int x = tid; x < CC * CC; x += CT) {
+            const int t = x / CC, j = x % CC;
+            const float r = j <= t ? expf(G[t] - G[j]) : 0.0f;
+            m.qk[t * LA + j] = m.qk[t * LA + j] * r;                             // r(t, j) (q_t . k_j), j <= t
+            m.kk[t * LA + j] = j < t ? beta[t] * r * m.kk[t * LA + j] : 0.0f;    // beta_t r(t, j) (k_t . k_j), j < t
+        }
+        // what S0 gives token ot, columns oc .. oc + 3: to the right-hand side of the system and to the read-out
+        float o[4] = {0.0f, 0.0f, 0.0f, 0.0f}, bk[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        {
+            const float* qrow = m.q + ot * ldq;
+            const float* krow = m.k + ot * ldq;
+            for (int i = 0; i < dp; i++) {
+                const float qi = qrow[i], ki = krow[i];
+                const float4 sv = *reinterpret_cast<const float4*>(m.s0 + i * COLS + oc);
+                o[0] = fmaf(qi, sv.x, o[0]); o[1] = fmaf(qi, sv.y, o[1]); o[2] = fmaf(qi, sv.z, o[2]); o[3] = fmaf(qi, sv.w, o[3]);
+                bk[0] = fmaf(ki, sv.x, bk[0]); bk[1] = fmaf(ki, sv.y, bk[1]); bk[2] = fmaf(ki, sv.z, bk[2]); bk[3] = fmaf(ki, sv.w, bk[3]);
+            }
+            const float gt = expf(G[ot]);
+            float4 vv = *reinterpret_cast<const float4*>(m.v + ot * COLS + oc);
+            vv.x = beta[ot] * (vv.x - gt * bk[0]); vv.y = beta[ot] * (vv.y - gt * bk[1]);
+            vv.z = beta[ot] * (vv.z - gt * bk[2]); vv.w = beta[ot] * (vv.w - gt * bk[3]);
+            o[0] *= gt; o[1] *= gt; o[2] *= gt; o[3] *= gt;
+            *reinterpret_cast<float4*>(m.v + ot * COLS + oc) = vv;              // each thread reads and writes its own four
+        }
+        __syncthreads();
+        if (tid < COLS) {                                 // the triangular system, a column a thread, rows in order
+            for (int t = 1; t < CC; t++) {
+                const float* lrow = m.kk + t * LA;
+                float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+                int j = 0;
+                for (; j + 3 < t; j += 4) {
+                    a0 = fmaf(lrow[j], m.v[j * COLS + tid], a0);
+                    a1 = fmaf(lrow[j + 1], m.v[(j + 1) * COLS + tid], a1);
+                    a2 = fmaf(lrow[j + 2], m.v[(j + 2) * COLS + tid], a2);
+                    a3 = fmaf(lrow[j + 3], m.v[(j + 3) * COLS + tid], a3);
+                }
+                for (; j < t; j++) a0 = fmaf(lrow[j], m.v[j * COLS + tid], a0);
+                m.v[t * COLS + tid] -= (a0 + a1) + (a2 + a3);
+            }
+        }
+        __syncthreads();
+        {
+            const float* prow = m.qk + ot * LA;
+            for (int j = 0; j <= ot; j++) {
+                const float p = prow[j];
+                const float4 uu = *reinterpret_cast<const float4*>(m.v + j * COLS + oc);
+                o[0] = fmaf(p, uu.x, o[0]); o[1] = fmaf(p, uu.y, o[1]); o[2] = fmaf(p, uu.z, o[2]); o[3] = fmaf(p, uu.w, o[3]);
+            }
+            if (ot < n_tok)
+#pragma unroll
+                for (int c4 = 0; c4 < 4; c4++)
+                    if (col0 + oc + c4 < e) out[(size_t)(tc + ot) * ld_out + h * e + col0 + oc + c4] = o[c4];
+        }
+        constexpr int MAXR = 8;
+        float sn[MAXR][4];
+        const float G_last = G[CC - 1], g_all = expf(G_last);
+#pragma unroll
+        for (int r = 0; r < MAXR; r++) {
+            const int i = ot + 32 * r;
+            if (i < dp) {
+                const float4 sv = *reinterpret_cast<const float4*>(m.s0 + i * COLS + oc);
+                sn[r][0] = g_all * sv.x; sn[r][1] = g_all * sv.y; sn[r][2] = g_all * sv.z; sn[r][3] = g_all * sv.w;
+            }
+        }
+        for (int j = 0; j < CC; j++) {
+            const float w = expf(G_last - G[j]);
+            const float4 uu = *reinterpret_cast<const float4*>(m.v + j * COLS + oc);
+#pragma unroll
+            for (int r = 0; r < MAXR; r++) {
+                const int i = ot + 32 * r;
+                if (i < dp) {
+                    const float wk = w * m.k[j * ldq + i];
+                    sn[r][0] = fmaf(wk, uu.x, sn[r][0]); sn[r][1] = fmaf(wk, uu.y, sn[r][1]);
+                    sn[r][2] = fmaf(wk, uu.z, sn[r][2]); sn[r][3] = fmaf(wk, uu.w, sn[r][3]);
+                }
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < MAXR; r++) {
+            const int i = ot + 32 * r;
+            if (i < dp) *reinterpret_cast<float4*>(m.s0 + i * COLS + oc) = make_float4(sn[r][0], sn[r][1], sn[r][2], sn[r][3]);
+        }
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+    for (int x = tid; x < dp * COLS; x += CT) {
+        const int c = x / dp, i = x % dp;
+        if (i < d && col0 + c < e) S[(size_t)(col0 + c) * d + i] = m.s0[i * COLS + c];
+    }
+}
+
 size_t stage_bytes(int d) { return (size_t)CHUNK * (2 * d + COLS + 2) * sizeof(float); }
 
 }  // namespace
@@ -407,7 +796,7 @@ SANDY_API int sandy_conv_tail(const void* proj, int ld, int dtype, int channels,
 
 SANDY_API int sandy_delta_scan(const float* qkv, int ld, const float* bg, float* state, long long state_stride,
                                const int* q_start, const int* seq_slots, float* out, int ld_out, int n_seqs, int n_heads,
-                               int n_qk_heads, int qk_dim, int v_dim, cudaStream_t stream) {
+                               int n_qk_heads, int qk_dim, int v_dim, int long_from, cudaStream_t stream) {
     if (n_seqs == 0) return SANDY_OK;
     if (!qkv || !bg || !state || !q_start || !seq_slots || !out) return SANDY_ERR_ARGUMENT;
     if (qk_dim <= 0 || qk_dim > 256 || v_dim <= 0 || n_qk_heads <= 0 || n_heads % n_qk_heads) return SANDY_ERR_UNSUPPORTED;
@@ -416,7 +805,7 @@ SANDY_API int sandy_delta_scan(const float* qkv, int ld, const float* bg, float*
 #define CASE(RR)                                                                                                       \
     if (qk_dim <= 32 * RR)                                                                                             \
         return sandy_launch(delta_scan_kernel<RR>, grid, dim3(THREADS), smem, stream, qkv, ld, bg, state, state_stride, \
-                            q_start, seq_slots, out, ld_out, n_heads, n_qk_heads, qk_dim, v_dim)
+                            q_start, seq_slots, out, ld_out, n_heads, n_qk_heads, qk_dim, v_dim, long_from)
     CASE(1); CASE(2); CASE(3); CASE(4); CASE(6); CASE(8);
 #undef CASE
     return SANDY_ERR_UNSUPPORTED;
@@ -425,7 +814,7 @@ SANDY_API int sandy_delta_scan(const float* qkv, int ld, const float* bg, float*
 SANDY_API int sandy_mlstm_scan(const void* proj, int ld, int dtype, int q_off, int k_off, int v_off, const float* gates,
                                int ld_gates, const float* gate_bias, float cap, float q_scale, float* state,
                                long long state_stride, const int* q_start, const int* seq_slots, float* out, int ld_out,
-                               int n_seqs, int n_heads, int qk_dim, int v_dim, cudaStream_t stream) {
+                               int n_seqs, int n_heads, int qk_dim, int v_dim, int long_from, cudaStream_t stream) {
     if (n_seqs == 0) return SANDY_OK;
     if (!proj || !gates || !gate_bias || !state || !q_start || !seq_slots || !out) return SANDY_ERR_ARGUMENT;
     if (qk_dim <= 0 || qk_dim > 256 || v_dim <= 0 || !(cap > 0.0f)) return SANDY_ERR_UNSUPPORTED;
@@ -435,9 +824,57 @@ SANDY_API int sandy_mlstm_scan(const void* proj, int ld, int dtype, int q_off, i
     if (qk_dim <= 32 * RR)                                                                                               \
         return sandy_launch(mlstm_scan_kernel<TT, RR>, grid, dim3(THREADS), smem, stream, (const TT*)proj, ld, q_off,    \
                             k_off, v_off, gates, ld_gates, gate_bias, cap, q_scale, state, state_stride, q_start,        \
-                            seq_slots, out, ld_out, n_heads, qk_dim, v_dim)
+                            seq_slots, out, ld_out, n_heads, qk_dim, v_dim, long_from)
     if (dtype == SANDY_F32) { CASE(float, 1); CASE(float, 2); CASE(float, 3); CASE(float, 4); CASE(float, 6); CASE(float, 8); }
     if (dtype == SANDY_BF16) { CASE(bf16, 1); CASE(bf16, 2); CASE(bf16, 3); CASE(bf16, 4); CASE(bf16, 6); CASE(bf16, 8); }
 #undef CASE
+    return SANDY_ERR_UNSUPPORTED;
+}
+
+// The chunked forms: only requests that bring at least `long_from` tokens (the token-by-token kernels above, given
+// the same number, take the others).  Arguments as sandy_delta_scan / sandy_mlstm_scan.
+SANDY_API int sandy_delta_chunk_scan(const float* qkv, int ld, const float* bg, float* state, long long state_stride,
+                                     const int* q_start, const int* seq_slots, float* out, int ld_out, int n_seqs, int n_heads,
+                                     int n_qk_heads, int qk_dim, int v_dim, int long_from, cudaStream_t stream) {
+    if (n_seqs == 0) return SANDY_OK;
+    if (!qkv || !bg || !state || !q_start || !seq_slots || !out) return SANDY_ERR_ARGUMENT;
+    if (qk_dim <= 0 || qk_dim > 256 || v_dim <= 0 || n_qk_heads <= 0 || n_heads % n_qk_heads || long_from < 1) return SANDY_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(qkv) & 3) || (reinterpret_cast<uintptr_t>(state) & 3)) return SANDY_ERR_UNSUPPORTED;
+    const size_t smem = chunk_smem_bytes(qk_dim, true);
+    static size_t configured = 0;
+    if (smem > 48 * 1024 && smem > configured) {
+        cudaError_t err = cudaFuncSetAttribute(delta_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) return (int)err;
+        configured = smem;
+    }
+    const dim3 grid(n_seqs, n_heads, (v_dim + COLS - 1) / COLS);
+    return sandy_launch(delta_chunk_kernel, grid, dim3(CT), smem, stream, qkv, ld, bg, state, state_stride, q_start, seq_slots, out,
+                        ld_out, n_heads, n_qk_heads, qk_dim, v_dim, long_from);
+}
+
+SANDY_API int sandy_mlstm_chunk_scan(const void* proj, int ld, int dtype, int q_off, int k_off, int v_off, const float* gates,
+                                     int ld_gates, const float* gate_bias, float cap, float q_scale, float* state,
+                                     long long state_stride, const int* q_start, const int* seq_slots, float* out, int ld_out,
+                                     int n_seqs, int n_heads, int qk_dim, int v_dim, int long_from, cudaStream_t stream) {
+    if (n_seqs == 0) return SANDY_OK;
+    if (!proj || !gates || !gate_bias || !state || !q_start || !seq_slots || !out) return SANDY_ERR_ARGUMENT;
+    if (qk_dim <= 0 || qk_dim > 256 || v_dim <= 0 || !(cap > 0.0f) || long_from < 1) return SANDY_ERR_UNSUPPORTED;
+    const size_t smem = chunk_smem_bytes(qk_dim, false);
+    const dim3 grid(n_seqs, n_heads, (v_dim + COLS - 1) / COLS);
+#define GO(TT)                                                                                                            \
+    do {                                                                                                                  \
+        static size_t configured = 0;                                                                                     \
+        if (smem > 48 * 1024 && smem > configured) {                                                                      \
+            cudaError_t err = cudaFuncSetAttribute(mlstm_chunk_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (err != cudaSuccess) return (int)err;                                                                      \
+            configured = smem;                                                                                            \
+        }                                                                                                                 \
+        return sandy_launch(mlstm_chunk_kernel<TT>, grid, dim3(CT), smem, stream, (const TT*)proj, ld, q_off, k_off, v_off, gates, \
+                            ld_gates, gate_bias, cap, q_scale, state, state_stride, q_start, seq_slots, out, ld_out, n_heads, \
+                            qk_dim, v_dim, long_from);                                                                    \
+    } while (0)
+    if (dtype == SANDY_F32) GO(float);
+    if (dtype == SANDY_BF16) GO(bf16);
+#undef GO
     return SANDY_ERR_UNSUPPORTED;
 }

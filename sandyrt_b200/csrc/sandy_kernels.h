@@ -173,11 +173,18 @@ int sandy_conv_tail(const void* proj, int ld, int dtype, int channels, int n_tap
                     long long tail_off, const int* q_start, const int* seq_slots, int n_seqs, cudaStream_t stream);
 int sandy_delta_scan(const float* qkv, int ld, const float* bg, float* state, long long state_stride, const int* q_start,
                      const int* seq_slots, float* out, int ld_out, int n_seqs, int n_heads, int n_qk_heads, int qk_dim,
-                     int v_dim, cudaStream_t stream);
+                     int v_dim, int long_from, cudaStream_t stream);
+int sandy_delta_chunk_scan(const float* qkv, int ld, const float* bg, float* state, long long state_stride,
+                           const int* q_start, const int* seq_slots, float* out, int ld_out, int n_seqs, int n_heads,
+                           int n_qk_heads, int qk_dim, int v_dim, int long_from, cudaStream_t stream);
 int sandy_mlstm_scan(const void* proj, int ld, int dtype, int q_off, int k_off, int v_off, const float* gates, int ld_gates,
                      const float* gate_bias, float cap, float q_scale, float* state, long long state_stride,
                      const int* q_start, const int* seq_slots, float* out, int ld_out, int n_seqs, int n_heads, int qk_dim,
-                     int v_dim, cudaStream_t stream);
+                     int v_dim, int long_from, cudaStream_t stream);
+int sandy_mlstm_chunk_scan(const void* proj, int ld, int dtype, int q_off, int k_off, int v_off, const float* gates,
+                           int ld_gates, const float* gate_bias, float cap, float q_scale, float* state,
+                           long long state_stride, const int* q_start, const int* seq_slots, float* out, int ld_out,
+                           int n_seqs, int n_heads, int qk_dim, int v_dim, int long_from, cudaStream_t stream);
 
 /* sampling.cu */
 int sandy_sample(const float* logits, int ld, int n_rows, int vocab, const float* temperature, const int* top_k,
