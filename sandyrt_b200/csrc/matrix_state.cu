@@ -385,7 +385,8 @@ constexpr int CC = 32;                 // tokens per chunk
 constexpr int CT = 128;                // threads
 constexpr int LA = CC + 4;             // row pitch of the CC x CC matrices
 
-// X Y^T for a tile of 2 rows of X and 4 rows of Y, rows of `len` floats (a multiple of 4) at pitch ld.
+// X Y^T for 2 rows of X (16 rows apart) and 4 rows of Y (8 rows apart), rows of `len` floats (a multiple of 4) at
+// pitch ld.  A warp's threads then read neighbouring rows, which lie in different banks (the pitch is 4 mod 32).
 __device__ __forceinline__ void tile_2x4(const float* __restrict__ X, const float* __restrict__ Y, int ld, int len,
                                          float (&acc)[2][4]) {
 #pragma unroll
@@ -395,9 +396,9 @@ __device__ __forceinline__ void tile_2x4(const float* __restrict__ X, const floa
     for (int i = 0; i < len; i += 4) {
         float4 x[2], y[4];
 #pragma unroll
-        for (int a = 0; a < 2; a++) x[a] = *reinterpret_cast<const float4*>(X + a * ld + i);
+        for (int a = 0; a < 2; a++) x[a] = *reinterpret_cast<const float4*>(X + a * 16 * ld + i);
 #pragma unroll
-        for (int b = 0; b < 4; b++) y[b] = *reinterpret_cast<const float4*>(Y + b * ld + i);
+        for (int b = 0; b < 4; b++) y[b] = *reinterpret_cast<const float4*>(Y + b * 8 * ld + i);
 #pragma unroll
         for (int a = 0; a < 2; a++)
 #pragma unroll
@@ -434,13 +435,37 @@ size_t chunk_smem_bytes(int d, bool two) {
     return (size_t)(2 * CC * (dp + 4) + CC * COLS + (two ? 2 : 1) * CC * LA + dp * COLS + dp + 4 * CC) * sizeof(float);
 }
 
-template <typename T>
+// Inclusive running sum / maximum over the 32 lanes of a warp.
+__device__ __forceinline__ float warp_scan_sum(float v, int lane) {
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float u = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += u;
+    }
+    return v;
+}
+__device__ __forceinline__ float warp_scan_max(float v, int lane) {
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float u = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v = fmaxf(v, u);
+    }
+    return v;
+}
+static_assert(CC == 32, "the running sums of a chunk are one warp's scan");
+
+// DPMAX: the head's query/key size rounded up to 32, 64, 128 or 256.  Up to 128 a thread holds its share of the next
+// chunk's queries and keys in registers while this chunk is computed (NPRE of them: 2 * CC * dp <= NPRE * CT); wider
+// heads are staged when their chunk begins.  MAXR: rows of the state a thread owns.
+template <typename T, int DPMAX>
 __global__ void __launch_bounds__(CT)
 mlstm_chunk_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ gates,
                    int ld_gates, const float* __restrict__ gate_bias, float cap, float q_scale, float* __restrict__ state,
                    long long state_stride, const int* __restrict__ q_start, const int* __restrict__ seq_slots,
                    float* __restrict__ out, int ld_out, int n_heads, int d, int e, int long_from) {
     extern __shared__ __align__(16) float chunk_raw[];
+    constexpr int NPRE = DPMAX <= 128 ? 2 * CC * DPMAX / CT : 0;
+    constexpr int MAXR = DPMAX / 32;
     const int s = blockIdx.x, h = blockIdx.y, z = blockIdx.z, col0 = z * COLS, Z = gridDim.z;
     const int t0 = q_start[s], t1 = q_start[s + 1];
     if (t1 - t0 < long_from) return;
@@ -466,46 +491,79 @@ mlstm_chunk_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int
     if (tid == 0) m0_s = *m_st;
     const int tr = tid / 8, tc4 = tid % 8;               // this thread's 2 x 4 tile of q k^T
     const int ot = tid / 4, oc = (tid % 4) * 4;          // this thread's token and four columns of the read-out
+    // the next chunk's inputs wait in registers while this chunk is computed
+    // (as loaded: an instruction that used a value here would make the warp wait for it)
+    T pre_qk[NPRE > 0 ? NPRE : 1], pre_v[CC * COLS / CT];
+    float pre_g[2];
+    auto fetch = [&](int tcn) {
+        const int n_tok = min(CC, t1 - tcn);              // <= 0 behind the last chunk: nothing is read
+#pragma unroll
+        for (int u = 0; u < NPRE; u++) {
+            const int x = tid + u * CT;
+            const int which = x / (CC * dp), rem = x % (CC * dp);
+            const int t = rem / dp, i = rem % dp;
+            T v = from_f32<T>(0.0f);
+            if (which < 2 && t < n_tok && i < d) v = proj[(size_t)(tcn + t) * ld + (which == 0 ? q_off : k_off) + h * d + i];
+            pre_qk[u] = v;
+        }
+#pragma unroll
+        for (int u = 0; u < CC * COLS / CT; u++) {
+            const int x = tid + u * CT;
+            const int t = x / COLS, c = x % COLS;
+            T v = from_f32<T>(0.0f);
+            if (t < n_tok && col0 + c < e) v = proj[(size_t)(tcn + t) * ld + v_off + h * e + col0 + c];
+            pre_v[u] = v;
+        }
+        pre_g[0] = pre_g[1] = 0.0f;
+        if (tid < CC && tid < n_tok) {
+            const float* g = gates + (size_t)(tcn + tid) * ld_gates;
+            pre_g[0] = g[h];
+            pre_g[1] = g[n_heads + h];
+        }
+    };
+    fetch(t0);
     for (int tc = t0; tc < t1; tc += CC) {
         const int n_tok = min(CC, t1 - tc);
         __syncthreads();
-        for (int x = tid; x < CC * dp; x += CT) {
-            const int t = x / dp, i = x % dp;
-            const bool live = t < n_tok && i < d;
-            const T* row = proj + (size_t)(tc + t) * ld;
-            m.q[t * ldq + i] = live ? to_f32(row[q_off + h * d + i]) * q_scale : 0.0f;
-            m.k[t * ldq + i] = live ? to_f32(row[k_off + h * d + i]) : 0.0f;
+#pragma unroll
+        for (int u = 0; u < NPRE; u++) {
+            const int x = tid + u * CT;
+            const int which = x / (CC * dp), rem = x % (CC * dp);
+            if (which < 2) (which == 0 ? m.q : m.k)[(rem / dp) * ldq + rem % dp] = to_f32(pre_qk[u]) * (which == 0 ? q_scale : 1.0f);
         }
-        for (int x = tid; x < CC * COLS; x += CT) {
-            const int t = x / COLS, c = x % COLS;
-            m.v[x] = (t < n_tok && col0 + c < e) ? to_f32(proj[(size_t)(tc + t) * ld + v_off + h * e + col0 + c]) : 0.0f;
-        }
+        if (NPRE == 0)
+            for (int x = tid; x < CC * dp; x += CT) {
+                const int t = x / dp, i = x % dp;
+                const bool live = t < n_tok && i < d;
+                const T* row = proj + (size_t)(tc + t) * ld;
+                m.q[t * ldq + i] = live ? to_f32(row[q_off + h * d + i]) * q_scale : 0.0f;
+                m.k[t * ldq + i] = live ? to_f32(row[k_off + h * d + i]) : 0.0f;
+            }
+#pragma unroll
+        for (int u = 0; u < CC * COLS / CT; u++) m.v[tid + u * CT] = to_f32(pre_v[u]);
         if (tid < CC) {
             const bool live = tid < n_tok;
-            const float* g = gates + (size_t)(tc + tid) * ld_gates;
-            li[tid] = live ? cap * tanhf((g[h] + bias_i) / cap) : -INFINITY;
-            Fs[tid] = live ? log_sigmoid_f(cap * tanhf((g[n_heads + h] + bias_f) / cap)) : 0.0f;
+            li[tid] = live ? cap * tanhf((pre_g[0] + bias_i) / cap) : -INFINITY;
+            Fs[tid] = live ? log_sigmoid_f(cap * tanhf((pre_g[1] + bias_f) / cap)) : 0.0f;
         }
         __syncthreads();
-        if (tid == 0) {                                   // the running sums and maxima, one after the other
-            float F = 0.0f, M = m0_s;
-            for (int t = 0; t < CC; t++) {
-                F += Fs[t];
-                const float a = li[t] - F;
-                M = fmaxf(M, a);
-                li[t] = a;
-                Fs[t] = F;
-                Ms[t] = M;
-                cw[t] = expf(m0_s - M);
-            }
+        fetch(tc + CC);
+        if (tid < CC) {                                   // the running sums and maxima: one warp's scans
+            const float F = warp_scan_sum(Fs[tid], tid);
+            const float a = li[tid] - F;
+            const float M = fmaxf(warp_scan_max(a, tid), m0_s);
+            li[tid] = a;
+            Fs[tid] = F;
+            Ms[tid] = M;
+            cw[tid] = expf(m0_s - M);
         }
         {
             float acc[2][4];
-            tile_2x4(m.q + (2 * tr) * ldq, m.k + (4 * tc4) * ldq, ldq, dp, acc);
+            tile_2x4(m.q + tr * ldq, m.k + tc4 * ldq, ldq, dp, acc);
 #pragma unroll
             for (int a = 0; a < 2; a++)
 #pragma unroll
-                for (int b = 0; b < 4; b++) m.qk[(2 * tr + a) * LA + 4 * tc4 + b] = acc[a][b];
+                for (int b = 0; b < 4; b++) m.qk[(tr + 16 * a) * LA + tc4 + 8 * b] = acc[a][b];
         }
         __syncthreads();
         for (int x = tid; x < CC * CC; x += CT) {         // weights: w(t, j) (q_t . k_j), zero above the diagonal
@@ -540,7 +598,6 @@ mlstm_chunk_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int
             }
         }
         // the state after the chunk: rows i = ot, ot + 32, ..., columns oc .. oc + 3 (kept in registers until everyone has read S0)
-        constexpr int MAXR = 8;                           // rows of the state a thread owns: d <= 256
         float sn[MAXR][4], nn[MAXR];
         const float c_last = cw[CC - 1], M_last = Ms[CC - 1];
 #pragma unroll
@@ -588,11 +645,14 @@ mlstm_chunk_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int
     if (tid == 0) *m_st = m0_s;
 }
 
+template <int DPMAX>
 __global__ void __launch_bounds__(CT)
 delta_chunk_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ bg, float* __restrict__ state,
                    long long state_stride, const int* __restrict__ q_start, const int* __restrict__ seq_slots,
                    float* __restrict__ out, int ld_out, int n_heads, int n_qk_heads, int d, int e, int long_from) {
     extern __shared__ __align__(16) float chunk_raw[];
+    constexpr int NPRE = DPMAX <= 128 ? 2 * CC * DPMAX / CT : 0;
+    constexpr int MAXR = DPMAX / 32;
     const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * COLS;
     const int t0 = q_start[s], t1 = q_start[s + 1];
     if (t1 - t0 < long_from) return;
@@ -610,45 +670,68 @@ delta_chunk_kernel(const float* __restrict__ qkv, int ld, const float* __restric
     }
     const int tr = tid / 8, tc4 = tid % 8;
     const int ot = tid / 4, oc = (tid % 4) * 4;
+    float pre_qk[NPRE > 0 ? NPRE : 1], pre_v[CC * COLS / CT], pre_g[2];
+    auto fetch = [&](int tcn) {
+        const int n_tok = min(CC, t1 - tcn);
+#pragma unroll
+        for (int u = 0; u < NPRE; u++) {
+            const int x = tid + u * CT;
+            const int which = x / (CC * dp), rem = x % (CC * dp);
+            const int t = rem / dp, i = rem % dp;
+            float v = 0.0f;
+            if (which < 2 && t < n_tok && i < d) v = qkv[(size_t)(tcn + t) * ld + (which * n_qk_heads + qh) * d + i];
+            pre_qk[u] = v;
+        }
+#pragma unroll
+        for (int u = 0; u < CC * COLS / CT; u++) {
+            const int x = tid + u * CT;
+            const int t = x / COLS, c = x % COLS;
+            pre_v[u] = (t < n_tok && col0 + c < e) ? qkv[(size_t)(tcn + t) * ld + 2 * n_qk_heads * d + h * e + col0 + c] : 0.0f;
+        }
+        pre_g[0] = pre_g[1] = 0.0f;
+        if (tid < CC && tid < n_tok) {
+            pre_g[0] = bg[(size_t)(tcn + tid) * 2 * n_heads + h];
+            pre_g[1] = bg[(size_t)(tcn + tid) * 2 * n_heads + n_heads + h];
+        }
+    };
+    fetch(t0);
     for (int tc = t0; tc < t1; tc += CC) {
         const int n_tok = min(CC, t1 - tc);
         __syncthreads();
-        for (int x = tid; x < CC * dp; x += CT) {
-            const int t = x / dp, i = x % dp;
-            const bool live = t < n_tok && i < d;
-            const float* row = qkv + (size_t)(tc + t) * ld;
-            m.q[t * ldq + i] = live ? row[qh * d + i] : 0.0f;
-            m.k[t * ldq + i] = live ? row[(n_qk_heads + qh) * d + i] : 0.0f;
+#pragma unroll
+        for (int u = 0; u < NPRE; u++) {
+            const int x = tid + u * CT;
+            const int which = x / (CC * dp), rem = x % (CC * dp);
+            if (which < 2) (which == 0 ? m.q : m.k)[(rem / dp) * ldq + rem % dp] = pre_qk[u];
         }
-        for (int x = tid; x < CC * COLS; x += CT) {
-            const int t = x / COLS, c = x % COLS;
-            m.v[x] = (t < n_tok && col0 + c < e) ? qkv[(size_t)(tc + t) * ld + 2 * n_qk_heads * d + h * e + col0 + c] : 0.0f;
-        }
+        if (NPRE == 0)
+            for (int x = tid; x < CC * dp; x += CT) {
+                const int t = x / dp, i = x % dp;
+                const bool live = t < n_tok && i < d;
+                const float* row = qkv + (size_t)(tc + t) * ld;
+                m.q[t * ldq + i] = live ? row[qh * d + i] : 0.0f;
+                m.k[t * ldq + i] = live ? row[(n_qk_heads + qh) * d + i] : 0.0f;
+            }
+#pragma unroll
+        for (int u = 0; u < CC * COLS / CT; u++) m.v[tid + u * CT] = pre_v[u];
         if (tid < CC) {
-            const bool live = tid < n_tok;
-            beta[tid] = live ? bg[(size_t)(tc + tid) * 2 * n_heads + h] : 0.0f;
-            G[tid] = live ? bg[(size_t)(tc + tid) * 2 * n_heads + n_heads + h] : 0.0f;
+            beta[tid] = pre_g[0];
+            G[tid] = warp_scan_sum(pre_g[1], tid);        // running sum of the decays' logarithms
         }
         __syncthreads();
-        if (tid == 0) {
-            float acc = 0.0f;
-            for (int t = 0; t < CC; t++) {
-                acc += G[t];
-                G[t] = acc;
-            }
-        }
+        fetch(tc + CC);
         {
             float acc[2][4];
-            tile_2x4(m.q + (2 * tr) * ldq, m.k + (4 * tc4) * ldq, ldq, dp, acc);
+            tile_2x4(m.q + tr * ldq, m.k + tc4 * ldq, ldq, dp, acc);
 #pragma unroll
             for (int a = 0; a < 2; a++)
 #pragma unroll
-                for (int b = 0; b < 4; b++) m.qk[(2 * tr + a) * LA + 4 * tc4 + b] = acc[a][b];
-            tile_2x4(m.k + (2 * tr) * ldq, m.k + (4 * tc4) * ldq, ldq, dp, acc);
+                for (int b = 0; b < 4; b++) m.qk[(tr + 16 * a) * LA + tc4 + 8 * b] = acc[a][b];
+            tile_2x4(m.k + tr * ldq, m.k + tc4 * ldq, ldq, dp, acc);
 #pragma unroll
             for (int a = 0; a < 2; a++)
 #pragma unroll
-                for (int b = 0; b < 4; b++) m.kk[(2 * tr + a) * LA + 4 * tc4 + b] = acc[a][b];
+                for (int b = 0; b < 4; b++) m.kk[(tr + 16 * a) * LA + tc4 + 8 * b] = acc[a][b];
         }
         __syncthreads();
         for (int x = tid; x < CC * CC; x += CT) {
@@ -704,7 +787,6 @@ delta_chunk_kernel(const float* __restrict__ qkv, int ld, const float* __restric
                 for (int c4 = 0; c4 < 4; c4++)
                     if (col0 + oc + c4 < e) out[(size_t)(tc + ot) * ld_out + h * e + col0 + oc + c4] = o[c4];
         }
-        constexpr int MAXR = 8;
         float sn[MAXR][4];
         const float G_last = G[CC - 1], g_all = expf(G_last);
 #pragma unroll
@@ -841,15 +923,24 @@ SANDY_API int sandy_delta_chunk_scan(const float* qkv, int ld, const float* bg, 
     if (qk_dim <= 0 || qk_dim > 256 || v_dim <= 0 || n_qk_heads <= 0 || n_heads % n_qk_heads || long_from < 1) return SANDY_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(qkv) & 3) || (reinterpret_cast<uintptr_t>(state) & 3)) return SANDY_ERR_UNSUPPORTED;
     const size_t smem = chunk_smem_bytes(qk_dim, true);
-    static size_t configured = 0;
-    if (smem > 48 * 1024 && smem > configured) {
-        cudaError_t err = cudaFuncSetAttribute(delta_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (err != cudaSuccess) return (int)err;
-        configured = smem;
-    }
     const dim3 grid(n_seqs, n_heads, (v_dim + COLS - 1) / COLS);
-    return sandy_launch(delta_chunk_kernel, grid, dim3(CT), smem, stream, qkv, ld, bg, state, state_stride, q_start, seq_slots, out,
-                        ld_out, n_heads, n_qk_heads, qk_dim, v_dim, long_from);
+#define GO(DPMAX)                                                                                                         \
+    do {                                                                                                                  \
+        auto kern = delta_chunk_kernel<DPMAX>;                                                              \
+        static size_t configured = 0;                                                                                     \
+        if (smem > 48 * 1024 && smem > configured) {                                                                      \
+            cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
+            if (err != cudaSuccess) return (int)err;                                                                      \
+            configured = smem;                                                                                            \
+        }                                                                                                                 \
+        return sandy_launch(kern, grid, dim3(CT), smem, stream, qkv, ld, bg, state, state_stride, q_start, seq_slots, out, \
+                            ld_out, n_heads, n_qk_heads, qk_dim, v_dim, long_from);                                       \
+    } while (0)
+    if (qk_dim <= 32) GO(32);
+    if (qk_dim <= 64) GO(64);
+    if (qk_dim <= 128) GO(128);
+    GO(256);
+#undef GO
 }
 
 SANDY_API int sandy_mlstm_chunk_scan(const void* proj, int ld, int dtype, int q_off, int k_off, int v_off, const float* gates,
@@ -861,20 +952,29 @@ SANDY_API int sandy_mlstm_chunk_scan(const void* proj, int ld, int dtype, int q_
     if (qk_dim <= 0 || qk_dim > 256 || v_dim <= 0 || !(cap > 0.0f) || long_from < 1) return SANDY_ERR_UNSUPPORTED;
     const size_t smem = chunk_smem_bytes(qk_dim, false);
     const dim3 grid(n_seqs, n_heads, (v_dim + COLS - 1) / COLS);
-#define GO(TT)                                                                                                            \
+#define GO(TT, DPMAX)                                                                                                     \
     do {                                                                                                                  \
+        auto kern = mlstm_chunk_kernel<TT, DPMAX>;                                                          \
         static size_t configured = 0;                                                                                     \
         if (smem > 48 * 1024 && smem > configured) {                                                                      \
-            cudaError_t err = cudaFuncSetAttribute(mlstm_chunk_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
             if (err != cudaSuccess) return (int)err;                                                                      \
             configured = smem;                                                                                            \
         }                                                                                                                 \
-        return sandy_launch(mlstm_chunk_kernel<TT>, grid, dim3(CT), smem, stream, (const TT*)proj, ld, q_off, k_off, v_off, gates, \
-                            ld_gates, gate_bias, cap, q_scale, state, state_stride, q_start, seq_slots, out, ld_out, n_heads, \
-                            qk_dim, v_dim, long_from);                                                                    \
+        return sandy_launch(kern, grid, dim3(CT), smem, stream, (const TT*)proj, ld, q_off, k_off, v_off, gates, ld_gates, \
+                            gate_bias, cap, q_scale, state, state_stride, q_start, seq_slots, out, ld_out, n_heads, qk_dim, \
+                            v_dim, long_from);                                                                            \
     } while (0)
-    if (dtype == SANDY_F32) GO(float);
-    if (dtype == SANDY_BF16) GO(bf16);
+#define SIZES(TT)                                                                                                         \
+    do {                                                                                                                  \
+        if (qk_dim <= 32) GO(TT, 32);                                                                                     \
+        if (qk_dim <= 64) GO(TT, 64);                                                                                     \
+        if (qk_dim <= 128) GO(TT, 128);                                                                                   \
+        GO(TT, 256);                                                                                                      \
+    } while (0)
+    if (dtype == SANDY_F32) SIZES(float);
+    if (dtype == SANDY_BF16) SIZES(bf16);
+#undef SIZES
 #undef GO
     return SANDY_ERR_UNSUPPORTED;
 }
