@@ -44,8 +44,10 @@ def run(model_dir: str, dtype_name: str, out_dir: str, max_tokens: int, lines,
     os.makedirs(out_dir, exist_ok=True)
     model = load_model(model_dir, device="cuda:0", dtype=dtype)
     # The pool holds `max_tokens` tokens, in whole pages.
-    engine = Engine(model, max_tokens=_round_up(max_tokens, page_size), page_size=page_size,
-                    max_requests=max_requests)
+    # a step may bring as many tokens as the pool holds (a whole prompt at once)
+    pool = _round_up(max_tokens, page_size)
+    engine = Engine(model, max_tokens=pool, page_size=page_size, max_requests=max_requests,
+                    max_step_tokens=max(2048, pool))
     for raw in lines:
         raw = raw.strip()
         if not raw:
