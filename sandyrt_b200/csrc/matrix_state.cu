@@ -382,32 +382,27 @@ mlstm_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int 
 // depend on the column: q . k, k . k).  Tokens beyond a request's last are given weights of zero (log i = -inf,
 // beta = 0) and decays of one, so that a partly filled chunk leaves the state where its last token left it.
 constexpr int CC = 32;                 // tokens per chunk
-constexpr int CT = 128;                // threads
+constexpr int CT = 256;                // threads: a token row of q k^T, two columns of a read-out each
 constexpr int LA = CC + 4;             // row pitch of the CC x CC matrices
 
-// X Y^T for 2 rows of X (16 rows apart) and 4 rows of Y (8 rows apart), rows of `len` floats (a multiple of 4) at
-// pitch ld.  A warp's threads then read neighbouring rows, which lie in different banks (the pitch is 4 mod 32).
-__device__ __forceinline__ void tile_2x4(const float* __restrict__ X, const float* __restrict__ Y, int ld, int len,
-                                         float (&acc)[2][4]) {
+// x . y_b for one row x and 4 rows y_b of Y that lie 8 rows apart, rows of `len` floats (a multiple of 4) at pitch
+// ld.  A warp's threads then read neighbouring rows of Y, which lie in different banks (the pitch is 4 mod 32).
+__device__ __forceinline__ void tile_1x4(const float* __restrict__ X, const float* __restrict__ Y, int ld, int len,
+                                         float (&acc)[4]) {
 #pragma unroll
-    for (int a = 0; a < 2; a++)
-#pragma unroll
-        for (int b = 0; b < 4; b++) acc[a][b] = 0.0f;
+    for (int b = 0; b < 4; b++) acc[b] = 0.0f;
     for (int i = 0; i < len; i += 4) {
-        float4 x[2], y[4];
-#pragma unroll
-        for (int a = 0; a < 2; a++) x[a] = *reinterpret_cast<const float4*>(X + a * 16 * ld + i);
+        const float4 x = *reinterpret_cast<const float4*>(X + i);
+        float4 y[4];
 #pragma unroll
         for (int b = 0; b < 4; b++) y[b] = *reinterpret_cast<const float4*>(Y + b * 8 * ld + i);
 #pragma unroll
-        for (int a = 0; a < 2; a++)
-#pragma unroll
-            for (int b = 0; b < 4; b++) {
-                acc[a][b] = fmaf(x[a].x, y[b].x, acc[a][b]);
-                acc[a][b] = fmaf(x[a].y, y[b].y, acc[a][b]);
-                acc[a][b] = fmaf(x[a].z, y[b].z, acc[a][b]);
-                acc[a][b] = fmaf(x[a].w, y[b].w, acc[a][b]);
-            }
+        for (int b = 0; b < 4; b++) {
+            acc[b] = fmaf(x.x, y[b].x, acc[b]);
+            acc[b] = fmaf(x.y, y[b].y, acc[b]);
+            acc[b] = fmaf(x.z, y[b].z, acc[b]);
+            acc[b] = fmaf(x.w, y[b].w, acc[b]);
+        }
     }
 }
 
@@ -458,7 +453,7 @@ static_assert(CC == 32, "the running sums of a chunk are one warp's scan");
 // chunk's queries and keys in registers while this chunk is computed (NPRE of them: 2 * CC * dp <= NPRE * CT); wider
 // heads are staged when their chunk begins.  MAXR: rows of the state a thread owns.
 template <typename T, int DPMAX>
-__global__ void __launch_bounds__(CT)
+__global__ void __launch_bounds__(CT)          // all registers: capped at 128 it ran at half the speed (343 against 190 us)
 mlstm_chunk_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ gates,
                    int ld_gates, const float* __restrict__ gate_bias, float cap, float q_scale, float* __restrict__ state,
                    long long state_stride, const int* __restrict__ q_start, const int* __restrict__ seq_slots,
@@ -489,8 +484,8 @@ mlstm_chunk_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int
     }
     for (int i = tid; i < dp; i += CT) m.n0[i] = i < d ? n_st[i] : 0.0f;
     if (tid == 0) m0_s = *m_st;
-    const int tr = tid / 8, tc4 = tid % 8;               // this thread's 2 x 4 tile of q k^T
-    const int ot = tid / 4, oc = (tid % 4) * 4;          // this thread's token and four columns of the read-out
+    const int tr = tid / 8, tc4 = tid % 8;               // this thread's row and four columns of q k^T
+    const int ot = tid / 8, oc = (tid % 8) * 2;          // this thread's token and two columns of the read-out
     // the next chunk's inputs wait in registers while this chunk is computed
     // (as loaded: an instruction that used a value here would make the warp wait for it)
     T pre_qk[NPRE > 0 ? NPRE : 1], pre_v[CC * COLS / CT];
@@ -558,12 +553,10 @@ mlstm_chunk_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int
             cw[tid] = expf(m0_s - M);
         }
         {
-            float acc[2][4];
-            tile_2x4(m.q + tr * ldq, m.k + tc4 * ldq, ldq, dp, acc);
+            float acc[4];
+            tile_1x4(m.q + tr * ldq, m.k + tc4 * ldq, ldq, dp, acc);
 #pragma unroll
-            for (int a = 0; a < 2; a++)
-#pragma unroll
-                for (int b = 0; b < 4; b++) m.qk[(tr + 16 * a) * LA + tc4 + 8 * b] = acc[a][b];
+            for (int b = 0; b < 4; b++) m.qk[tr * LA + tc4 + 8 * b] = acc[b];
         }
         __syncthreads();
         for (int x = tid; x < CC * CC; x += CT) {         // weights: w(t, j) (q_t . k_j), zero above the diagonal
@@ -571,54 +564,53 @@ mlstm_chunk_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int
             m.qk[t * LA + j] = j <= t ? m.qk[t * LA + j] * expf(li[j] - Ms[t]) : 0.0f;
         }
         __syncthreads();
-        // read-out of token ot, columns oc .. oc + 3
-        float o[4] = {0.0f, 0.0f, 0.0f, 0.0f}, nq = 0.0f;
+        // read-out of token ot, columns oc and oc + 1
+        float o[2] = {0.0f, 0.0f}, nq = 0.0f;
         {
             const float* qrow = m.q + ot * ldq;
             for (int i = 0; i < dp; i++) {
                 const float qi = qrow[i];
-                const float4 sv = *reinterpret_cast<const float4*>(m.s0 + i * COLS + oc);
-                o[0] = fmaf(qi, sv.x, o[0]); o[1] = fmaf(qi, sv.y, o[1]); o[2] = fmaf(qi, sv.z, o[2]); o[3] = fmaf(qi, sv.w, o[3]);
+                const float2 sv = *reinterpret_cast<const float2*>(m.s0 + i * COLS + oc);
+                o[0] = fmaf(qi, sv.x, o[0]); o[1] = fmaf(qi, sv.y, o[1]);
                 nq = fmaf(qi, m.n0[i], nq);
             }
             const float c = cw[ot];
-            o[0] *= c; o[1] *= c; o[2] *= c; o[3] *= c; nq *= c;
+            o[0] *= c; o[1] *= c; nq *= c;
             const float* prow = m.qk + ot * LA;
             for (int j = 0; j <= ot; j++) {
                 const float p = prow[j];
-                const float4 vv = *reinterpret_cast<const float4*>(m.v + j * COLS + oc);
-                o[0] = fmaf(p, vv.x, o[0]); o[1] = fmaf(p, vv.y, o[1]); o[2] = fmaf(p, vv.z, o[2]); o[3] = fmaf(p, vv.w, o[3]);
+                const float2 vv = *reinterpret_cast<const float2*>(m.v + j * COLS + oc);
+                o[0] = fmaf(p, vv.x, o[0]); o[1] = fmaf(p, vv.y, o[1]);
                 nq += p;
             }
             if (ot < n_tok) {
                 const float den = fmaxf(fabsf(nq), expf(-(Fs[ot] + Ms[ot]))) + 1e-6f;
 #pragma unroll
-                for (int c4 = 0; c4 < 4; c4++)
-                    if (col0 + oc + c4 < e) out[(size_t)(tc + ot) * ld_out + h * e + col0 + oc + c4] = o[c4] / den;
+                for (int c2 = 0; c2 < 2; c2++)
+                    if (col0 + oc + c2 < e) out[(size_t)(tc + ot) * ld_out + h * e + col0 + oc + c2] = o[c2] / den;
             }
         }
         // the state after the chunk: rows i = ot, ot + 32, ..., columns oc .. oc + 3 (kept in registers until everyone has read S0)
-        float sn[MAXR][4], nn[MAXR];
+        float sn[MAXR][2], nn[MAXR];
         const float c_last = cw[CC - 1], M_last = Ms[CC - 1];
 #pragma unroll
         for (int r = 0; r < MAXR; r++) {
             const int i = ot + 32 * r;
             if (i < dp) {
-                const float4 sv = *reinterpret_cast<const float4*>(m.s0 + i * COLS + oc);
-                sn[r][0] = c_last * sv.x; sn[r][1] = c_last * sv.y; sn[r][2] = c_last * sv.z; sn[r][3] = c_last * sv.w;
+                const float2 sv = *reinterpret_cast<const float2*>(m.s0 + i * COLS + oc);
+                sn[r][0] = c_last * sv.x; sn[r][1] = c_last * sv.y;
                 nn[r] = c_last * m.n0[i];
             }
         }
         for (int j = 0; j < CC; j++) {
             const float w = expf(li[j] - M_last);
-            const float4 vv = *reinterpret_cast<const float4*>(m.v + j * COLS + oc);
+            const float2 vv = *reinterpret_cast<const float2*>(m.v + j * COLS + oc);
 #pragma unroll
             for (int r = 0; r < MAXR; r++) {
                 const int i = ot + 32 * r;
                 if (i < dp) {
                     const float wk = w * m.k[j * ldq + i];
                     sn[r][0] = fmaf(wk, vv.x, sn[r][0]); sn[r][1] = fmaf(wk, vv.y, sn[r][1]);
-                    sn[r][2] = fmaf(wk, vv.z, sn[r][2]); sn[r][3] = fmaf(wk, vv.w, sn[r][3]);
                     nn[r] += wk;
                 }
             }
@@ -629,7 +621,7 @@ mlstm_chunk_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int
         for (int r = 0; r < MAXR; r++) {
             const int i = ot + 32 * r;
             if (i < dp) {
-                *reinterpret_cast<float4*>(m.s0 + i * COLS + oc) = make_float4(sn[r][0], sn[r][1], sn[r][2], sn[r][3]);
+                *reinterpret_cast<float2*>(m.s0 + i * COLS + oc) = make_float2(sn[r][0], sn[r][1]);
                 if (oc == 0) m.n0[i] = nn[r];
             }
         }
@@ -646,7 +638,7 @@ mlstm_chunk_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int
 }
 
 template <int DPMAX>
-__global__ void __launch_bounds__(CT)
+__global__ void __launch_bounds__(CT, 2)       // two blocks an SM: wide models have more blocks than SMs (1,000 -> 408 us at 24 heads)
 delta_chunk_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ bg, float* __restrict__ state,
                    long long state_stride, const int* __restrict__ q_start, const int* __restrict__ seq_slots,
                    float* __restrict__ out, int ld_out, int n_heads, int n_qk_heads, int d, int e, int long_from) {
@@ -669,7 +661,7 @@ delta_chunk_kernel(const float* __restrict__ qkv, int ld, const float* __restric
         m.s0[i * COLS + c] = (i < d && col0 + c < e) ? S[(size_t)(col0 + c) * d + i] : 0.0f;
     }
     const int tr = tid / 8, tc4 = tid % 8;
-    const int ot = tid / 4, oc = (tid % 4) * 4;
+    const int ot = tid / 8, oc = (tid % 8) * 2;
     float pre_qk[NPRE > 0 ? NPRE : 1], pre_v[CC * COLS / CT], pre_g[2];
     auto fetch = [&](int tcn) {
         const int n_tok = min(CC, t1 - tcn);
@@ -721,17 +713,13 @@ delta_chunk_kernel(const float* __restrict__ qkv, int ld, const float* __restric
         __syncthreads();
         fetch(tc + CC);
         {
-            float acc[2][4];
-            tile_2x4(m.q + tr * ldq, m.k + tc4 * ldq, ldq, dp, acc);
+            float acc[4];
+            tile_1x4(m.q + tr * ldq, m.k + tc4 * ldq, ldq, dp, acc);
 #pragma unroll
-            for (int a = 0; a < 2; a++)
+            for (int b = 0; b < 4; b++) m.qk[tr * LA + tc4 + 8 * b] = acc[b];
+            tile_1x4(m.k + tr * ldq, m.k + tc4 * ldq, ldq, dp, acc);
 #pragma unroll
-                for (int b = 0; b < 4; b++) m.qk[(tr + 16 * a) * LA + tc4 + 8 * b] = acc[a][b];
-            tile_2x4(m.k + tr * ldq, m.k + tc4 * ldq, ldq, dp, acc);
-#pragma unroll
-            for (int a = 0; a < 2; a++)
-#pragma unroll
-                for (int b = 0; b < 4; b++) m.kk[(tr + 16 * a) * LA + tc4 + 8 * b] = acc[a][b];
+            for (int b = 0; b < 4; b++) m.kk[tr * LA + tc4 + 8 * b] = acc[b];
         }
         __syncthreads();
         for (int x = tid; x < CC * CC; x += CT) {
@@ -740,73 +728,86 @@ delta_chunk_kernel(const float* __restrict__ qkv, int ld, const float* __restric
             m.qk[t * LA + j] = m.qk[t * LA + j] * r;                             // r(t, j) (q_t . k_j), j <= t
             m.kk[t * LA + j] = j < t ? beta[t] * r * m.kk[t * LA + j] : 0.0f;    // beta_t r(t, j) (k_t . k_j), j < t
         }
-        // what S0 gives token ot, columns oc .. oc + 3: to the right-hand side of the system and to the read-out
-        float o[4] = {0.0f, 0.0f, 0.0f, 0.0f}, bk[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        // what S0 gives token ot, columns oc and oc + 1: to the right-hand side of the system and to the read-out
+        float o[2] = {0.0f, 0.0f}, bk[2] = {0.0f, 0.0f};
         {
             const float* qrow = m.q + ot * ldq;
             const float* krow = m.k + ot * ldq;
             for (int i = 0; i < dp; i++) {
                 const float qi = qrow[i], ki = krow[i];
-                const float4 sv = *reinterpret_cast<const float4*>(m.s0 + i * COLS + oc);
-                o[0] = fmaf(qi, sv.x, o[0]); o[1] = fmaf(qi, sv.y, o[1]); o[2] = fmaf(qi, sv.z, o[2]); o[3] = fmaf(qi, sv.w, o[3]);
-                bk[0] = fmaf(ki, sv.x, bk[0]); bk[1] = fmaf(ki, sv.y, bk[1]); bk[2] = fmaf(ki, sv.z, bk[2]); bk[3] = fmaf(ki, sv.w, bk[3]);
+                const float2 sv = *reinterpret_cast<const float2*>(m.s0 + i * COLS + oc);
+                o[0] = fmaf(qi, sv.x, o[0]); o[1] = fmaf(qi, sv.y, o[1]);
+                bk[0] = fmaf(ki, sv.x, bk[0]); bk[1] = fmaf(ki, sv.y, bk[1]);
             }
             const float gt = expf(G[ot]);
-            float4 vv = *reinterpret_cast<const float4*>(m.v + ot * COLS + oc);
+            float2 vv = *reinterpret_cast<const float2*>(m.v + ot * COLS + oc);
             vv.x = beta[ot] * (vv.x - gt * bk[0]); vv.y = beta[ot] * (vv.y - gt * bk[1]);
-            vv.z = beta[ot] * (vv.z - gt * bk[2]); vv.w = beta[ot] * (vv.w - gt * bk[3]);
-            o[0] *= gt; o[1] *= gt; o[2] *= gt; o[3] *= gt;
-            *reinterpret_cast<float4*>(m.v + ot * COLS + oc) = vv;              // each thread reads and writes its own four
+            o[0] *= gt; o[1] *= gt;
+            *reinterpret_cast<float2*>(m.v + ot * COLS + oc) = vv;              // each thread reads and writes its own two
         }
         __syncthreads();
-        if (tid < COLS) {                                 // the triangular system, a column a thread, rows in order
-            for (int t = 1; t < CC; t++) {
-                const float* lrow = m.kk + t * LA;
-                float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
-                int j = 0;
-                for (; j + 3 < t; j += 4) {
-                    a0 = fmaf(lrow[j], m.v[j * COLS + tid], a0);
-                    a1 = fmaf(lrow[j + 1], m.v[(j + 1) * COLS + tid], a1);
-                    a2 = fmaf(lrow[j + 2], m.v[(j + 2) * COLS + tid], a2);
-                    a3 = fmaf(lrow[j + 3], m.v[(j + 3) * COLS + tid], a3);
+        // The triangular system u_t = b_t - sum_{j<t} L(t, j) u_j, eight rows at a time: what the rows solved so far
+        // give the next eight is subtracted by 128 threads at once; inside the eight, a column a thread, rows in order.
+        for (int r0 = 0; r0 < CC; r0 += 8) {
+            if (r0 > 0) {
+                if (tid < 8 * COLS) {
+                    const int t = r0 + tid / COLS, c = tid % COLS;
+                    const float* lrow = m.kk + t * LA;
+                    float a0 = 0.0f, a1 = 0.0f;
+                    for (int j = 0; j < r0; j += 2) {
+                        a0 = fmaf(lrow[j], m.v[j * COLS + c], a0);
+                        a1 = fmaf(lrow[j + 1], m.v[(j + 1) * COLS + c], a1);
+                    }
+                    m.v[t * COLS + c] -= a0 + a1;
                 }
-                for (; j < t; j++) a0 = fmaf(lrow[j], m.v[j * COLS + tid], a0);
-                m.v[t * COLS + tid] -= (a0 + a1) + (a2 + a3);
+                __syncthreads();
             }
+            if (tid < COLS) {
+                float u[8];
+                u[0] = m.v[r0 * COLS + tid];
+#pragma unroll
+                for (int a = 1; a < 8; a++) {
+                    const float* lrow = m.kk + (r0 + a) * LA + r0;
+                    float acc = 0.0f;
+#pragma unroll
+                    for (int b = 0; b < a; b++) acc = fmaf(lrow[b], u[b], acc);
+                    u[a] = m.v[(r0 + a) * COLS + tid] - acc;
+                    m.v[(r0 + a) * COLS + tid] = u[a];
+                }
+            }
+            __syncthreads();
         }
-        __syncthreads();
         {
             const float* prow = m.qk + ot * LA;
             for (int j = 0; j <= ot; j++) {
                 const float p = prow[j];
-                const float4 uu = *reinterpret_cast<const float4*>(m.v + j * COLS + oc);
-                o[0] = fmaf(p, uu.x, o[0]); o[1] = fmaf(p, uu.y, o[1]); o[2] = fmaf(p, uu.z, o[2]); o[3] = fmaf(p, uu.w, o[3]);
+                const float2 uu = *reinterpret_cast<const float2*>(m.v + j * COLS + oc);
+                o[0] = fmaf(p, uu.x, o[0]); o[1] = fmaf(p, uu.y, o[1]);
             }
             if (ot < n_tok)
 #pragma unroll
-                for (int c4 = 0; c4 < 4; c4++)
-                    if (col0 + oc + c4 < e) out[(size_t)(tc + ot) * ld_out + h * e + col0 + oc + c4] = o[c4];
+                for (int c2 = 0; c2 < 2; c2++)
+                    if (col0 + oc + c2 < e) out[(size_t)(tc + ot) * ld_out + h * e + col0 + oc + c2] = o[c2];
         }
-        float sn[MAXR][4];
+        float sn[MAXR][2];
         const float G_last = G[CC - 1], g_all = expf(G_last);
 #pragma unroll
         for (int r = 0; r < MAXR; r++) {
             const int i = ot + 32 * r;
             if (i < dp) {
-                const float4 sv = *reinterpret_cast<const float4*>(m.s0 + i * COLS + oc);
-                sn[r][0] = g_all * sv.x; sn[r][1] = g_all * sv.y; sn[r][2] = g_all * sv.z; sn[r][3] = g_all * sv.w;
+                const float2 sv = *reinterpret_cast<const float2*>(m.s0 + i * COLS + oc);
+                sn[r][0] = g_all * sv.x; sn[r][1] = g_all * sv.y;
             }
         }
         for (int j = 0; j < CC; j++) {
             const float w = expf(G_last - G[j]);
-            const float4 uu = *reinterpret_cast<const float4*>(m.v + j * COLS + oc);
+            const float2 uu = *reinterpret_cast<const float2*>(m.v + j * COLS + oc);
 #pragma unroll
             for (int r = 0; r < MAXR; r++) {
                 const int i = ot + 32 * r;
                 if (i < dp) {
                     const float wk = w * m.k[j * ldq + i];
                     sn[r][0] = fmaf(wk, uu.x, sn[r][0]); sn[r][1] = fmaf(wk, uu.y, sn[r][1]);
-                    sn[r][2] = fmaf(wk, uu.z, sn[r][2]); sn[r][3] = fmaf(wk, uu.w, sn[r][3]);
                 }
             }
         }
@@ -814,7 +815,7 @@ delta_chunk_kernel(const float* __restrict__ qkv, int ld, const float* __restric
 #pragma unroll
         for (int r = 0; r < MAXR; r++) {
             const int i = ot + 32 * r;
-            if (i < dp) *reinterpret_cast<float4*>(m.s0 + i * COLS + oc) = make_float4(sn[r][0], sn[r][1], sn[r][2], sn[r][3]);
+            if (i < dp) *reinterpret_cast<float2*>(m.s0 + i * COLS + oc) = make_float2(sn[r][0], sn[r][1]);
         }
     }
     __syncthreads();
