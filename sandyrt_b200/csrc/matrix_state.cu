@@ -17,7 +17,9 @@
 // reductions.  The tokens' inputs are staged through shared memory a chunk at a time, the next chunk's
 // loads in flight while the current one is computed.  The state is stored transposed, [head][column][row],
 // so that a lane's rows of a column are consecutive lanes' consecutive floats.  The matrix memory's n and m
-// are advanced by every column block for itself and therefore kept once per column block.
+// are advanced by every column block for itself and therefore kept once per column block.  That is the token-by-token
+// form, which decode steps and short portions take; requests that bring many tokens go through the chunked kernels
+// further down, which treat 32 tokens at once.
 //
 // Everything here is float32 arithmetic whatever the engine's compute type: gates, decays, exponentials,
 // unit norms, the state.  Inputs that come from a projection are read in the projection's type.
