@@ -158,7 +158,11 @@ std::vector<CacheSpec> cache_specs_from(const Json& j) {
     for (const Json& s : j.items()) {
         if (s.is_null()) { out.push_back(CacheSpec::none()); continue; }
         const std::string kind = s.at("kind").as_string();
-        if (kind == "paged") out.push_back(CacheSpec::paged((int)s.at("n_kv_heads").as_int(), (int)s.at("head_dim").as_int(), (int)geti(s, "window", 0)));
+        if (kind == "paged") {
+            CacheSpec p = CacheSpec::paged((int)s.at("n_kv_heads").as_int(), (int)s.at("head_dim").as_int(), (int)geti(s, "window", 0));
+            p.planes = (int)geti(s, "planes", 2) == 1 ? 1 : 2;
+            out.push_back(p);
+        }
         else if (kind == "state") {
             std::vector<int64_t> shape;
             for (const Json& d : s.at("shape").items()) shape.push_back(d.as_int());
@@ -184,6 +188,7 @@ Json layout_json(const CacheLayout& l) {
         e["n_kv_heads"] = g.spec.n_kv_heads;
         e["head_dim"] = g.spec.head_dim;
         e["window"] = g.spec.window;
+        e["planes"] = g.spec.planes;
         groups.push(e);
     }
     out["groups"] = groups;

@@ -19,6 +19,11 @@ CacheSpec CacheSpec::paged(int n_kv_heads, int head_dim, int window) {
     s.window = window;
     return s;
 }
+CacheSpec CacheSpec::paged_one_plane(int n_kv_heads, int head_dim, int window) {
+    CacheSpec s = paged(n_kv_heads, head_dim, window);
+    s.planes = 1;
+    return s;
+}
 CacheSpec CacheSpec::state(std::vector<int64_t> shape, DType dtype) {
     CacheSpec s;
     s.kind = Kind::State;
@@ -33,9 +38,14 @@ CacheSpec CacheSpec::paged_with_state(int n_kv_heads, int head_dim, int window, 
     s.state_dtype = dtype;
     return s;
 }
-CacheSpec CacheSpec::pages_only() const { return has_pages() ? paged(n_kv_heads, head_dim, window) : none(); }
+CacheSpec CacheSpec::pages_only() const {
+    if (!has_pages()) return none();
+    CacheSpec s = paged(n_kv_heads, head_dim, window);
+    s.planes = planes;
+    return s;
+}
 bool CacheSpec::operator==(const CacheSpec& o) const {
-    return kind == o.kind && n_kv_heads == o.n_kv_heads && head_dim == o.head_dim && window == o.window &&
+    return kind == o.kind && n_kv_heads == o.n_kv_heads && head_dim == o.head_dim && window == o.window && planes == o.planes &&
            state_shape == o.state_shape && state_dtype == o.state_dtype;
 }
 
@@ -263,7 +273,7 @@ DeviceCaches::DeviceCaches(const CacheLayout& layout, const std::vector<int>& pa
     : layout_(layout), pages_per_group_(pages_per_group), max_requests_(max_requests), dtype_(dtype) {
     for (size_t g = 0; g < layout.groups.size(); g++) {
         const CacheSpec& s = layout.groups[g].spec;
-        const size_t bytes = layout.groups[g].caches.size() * (size_t)pages_per_group[g] * 2 * (size_t)s.n_kv_heads *
+        const size_t bytes = layout.groups[g].caches.size() * (size_t)pages_per_group[g] * (size_t)s.planes * (size_t)s.n_kv_heads *
                              (size_t)layout.page_size * (size_t)s.head_dim * dtype_size(dtype);
         void* p = nullptr;
         cuda_ok(cudaMalloc(&p, std::max<size_t>(bytes, 16)), "allocating a cache arena");
@@ -294,11 +304,11 @@ KVView DeviceCaches::kv(int cache) const {
     const CacheSpec& s = layout_.groups[(size_t)g].spec;
     const size_t esz = dtype_size(dtype_);
     const size_t head_block = (size_t)s.n_kv_heads * (size_t)layout_.page_size * (size_t)s.head_dim;     // one of K or V of a page
-    const size_t page_elems = 2 * head_block;
+    const size_t page_elems = (size_t)s.planes * head_block;
     KVView v;
     char* base = (char*)arenas_[(size_t)g] + (size_t)i * (size_t)pages_per_group_[(size_t)g] * page_elems * esz;
     v.k = base;
-    v.v = base + head_block * esz;
+    v.v = s.planes == 2 ? base + head_block * esz : base;
     v.page_stride = (long long)page_elems;
     v.num_pages = pages_per_group_[(size_t)g];
     v.n_kv_heads = s.n_kv_heads;
@@ -362,7 +372,7 @@ int CacheManager::admit(RequestId rid) {
 size_t CacheManager::kv_bytes_per_token() const {
     size_t total = 0;
     for (const auto& g : alloc_->layout().groups)
-        total += g.caches.size() * 2 * (size_t)g.spec.n_kv_heads * (size_t)g.spec.head_dim * dtype_size(device_->dtype());
+        total += g.caches.size() * (size_t)g.spec.planes * (size_t)g.spec.n_kv_heads * (size_t)g.spec.head_dim * dtype_size(device_->dtype());
     return total;
 }
 

@@ -49,6 +49,10 @@ struct CacheSpec {
     // PagedKV: keys and values of every position (or of the last `window` positions) in pages
     int n_kv_heads = 0, head_dim = 0;
     int window = 0;                        // 0: all positions stay; n: only the last n are read
+    // 2: a page holds keys and values; 1: one plane only, and a view's values are its keys' own numbers
+    // (attention over a latent that is key and value at once: a head's output is then as wide as the keys
+    // and the caller keeps the columns that mean something)
+    int planes = 2;
     // State: a per-request state of fixed size (a recurrent state, a convolution tail, ...).  It
     // lives in the request's state slot and starts as zeros when the request is admitted.
     std::vector<int64_t> state_shape;
@@ -56,6 +60,7 @@ struct CacheSpec {
 
     static CacheSpec none() { return CacheSpec(); }
     static CacheSpec paged(int n_kv_heads, int head_dim, int window = 0);
+    static CacheSpec paged_one_plane(int n_kv_heads, int head_dim, int window = 0);
     static CacheSpec state(std::vector<int64_t> shape, DType dtype = DType::F32);
     static CacheSpec paged_with_state(int n_kv_heads, int head_dim, int window, std::vector<int64_t> shape, DType dtype = DType::F32);
     bool has_pages() const { return kind == Kind::PagedKV || kind == Kind::PagedState; }

@@ -227,6 +227,15 @@ std::map<std::string, Architecture>& table() {
             return describe_panupel(*g);
         };
         t[panupel.name] = std::move(panupel);
+        Architecture sovezen;
+        sovezen.name = SovezenConfig::kArchitecture;
+        sovezen.parse = [](const Json& raw) { return std::unique_ptr<ModelConfig>(new SovezenConfig(SovezenConfig::from_json(raw))); };
+        sovezen.describe = [](const ModelConfig& c) {
+            const auto* g = dynamic_cast<const SovezenConfig*>(&c);
+            if (!g) throw ConfigError("Sovezen was given another architecture's configuration");
+            return describe_sovezen(*g);
+        };
+        t[sovezen.name] = std::move(sovezen);
     });
     return t;
 }

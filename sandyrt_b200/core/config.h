@@ -84,6 +84,35 @@ public:
     void validate() const override;
 };
 
+// Sovezen's config.json (core/sovezen.cpp says what the keys mean): layers listed one by one, each an attention over
+// a latent of keys and values in one of two forms, beside a dense or routed feed-forward, or none.
+class SovezenConfig : public ModelConfig {
+public:
+    static constexpr const char* kArchitecture = "Sovezen";
+    struct Layer {
+        std::string type;                                   // "latent_attention" | "latent_attention_2"
+        int64_t heads = 0, dim = 0, vdim = 0, kv_rank = 0;
+        int64_t rot_dim = 0;                                // latent_attention: rotated entries of a head's query and key
+        int64_t q_rank = 0;                                 // latent_attention_2: size of the queries' own latent
+        double scale = 1.0;
+        int64_t rot_dims = 0;                               // how many of the rot_dim entries turn
+        double rot_base = 10000.0;
+        std::string mlp;                                    // "dense" | "moe" | "" (no feed-forward)
+        int64_t ff = 0;                                     // dense: inner size; moe: an expert's inner size
+        int64_t experts = 0, top = 0;
+        int64_t weights_of = -1;                            // >= 0: the layer whose tensors this one uses
+    };
+    int64_t vocab = 0, width = 0;
+    double norm_eps = 1e-6, logit_scale = 1.0;
+    std::vector<Layer> layers;
+
+    static SovezenConfig from_json(const Json& raw);
+    std::string architecture() const override { return kArchitecture; }
+    Json to_json() const override;
+    void validate() const override;
+    int owner(int layer) const;                             // the layer whose tensors `layer` uses (itself, mostly)
+};
+
 // A configuration of an architecture defined outside this library: its normalised config.json
 // as the architecture's own `parse` returned it.
 class ForeignConfig : public ModelConfig {
@@ -118,5 +147,6 @@ ModelSpec describe(const ModelConfig& cfg);
 
 ModelSpec describe_gpt2(const GPT2Config& cfg);
 ModelSpec describe_panupel(const PanupelConfig& cfg);
+ModelSpec describe_sovezen(const SovezenConfig& cfg);
 
 }  // namespace sandy

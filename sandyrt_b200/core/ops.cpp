@@ -624,6 +624,103 @@ void cast_cols(const Launch& l, const Tensor& x, Tensor& out) {
     check(fn((const float*)x.data, (int)x.ld, out.data, (int)out.ld, (int)x.rows, (int)x.cols, code_of(out.dtype), l.stream), "cast_cols");
 }
 
+void scale_add(const Launch& l, const Tensor& y, const Tensor& gain, const Tensor* y2, const Tensor* gain2, Tensor& x) {
+    if (x.dtype != DType::F32 || y.dtype != DType::F32 || gain.dtype != DType::F32 || y.rows != x.rows || y.cols != x.cols ||
+        gain.numel() != x.cols || (y2 && (!gain2 || y2->dtype != DType::F32 || gain2->dtype != DType::F32 || y2->rows != x.rows ||
+                                          y2->cols != x.cols || gain2->numel() != x.cols)))
+        throw KernelError("scale_add: float32 x and y of one shape, float32 gain [width] expected");
+    static auto fn = SANDY_KERNEL(elementwise, sandy_scale_add);
+    OpTimer timer(l, "layer scale + residual", (y2 ? 4.0 : 3.0) * tensor_bytes(&x), 0);
+    check(fn((const float*)y.data, (int)y.ld, (const float*)gain.data, y2 ? (const float*)y2->data : nullptr, y2 ? (int)y2->ld : 0,
+             y2 ? (const float*)gain2->data : nullptr, (float*)x.data, (int)x.ld, (int)x.rows, (int)x.cols, l.stream),
+          "scale_add");
+}
+
+void scale(const Launch& l, Tensor& x, float s) {
+    if (x.dtype != DType::F32 || !x.contiguous()) throw KernelError("scale: a dense float32 tensor expected");
+    static auto fn = SANDY_KERNEL(elementwise, sandy_scale_f32);
+    OpTimer timer(l, "scale", 2.0 * tensor_bytes(&x), 0);
+    check(fn((float*)x.data, (long long)x.numel(), s, l.stream), "scale");
+}
+
+void latent_prepare(const Launch& l, const LatentPrepare& p, const Tensor& down, const Tensor* q, const KVView& c,
+                    const int* block_table, int max_blocks, const int* token_seq, const int* positions, Tensor* q_latent,
+                    Tensor& q_abs) {
+    const int64_t T = down.rows;
+    if (down.dtype != DType::F32 || down.cols < p.q_rank + p.kv_rank + p.rot_dim || c.n_kv_heads != 1 || c.k != c.v ||
+        c.head_dim < p.kv_rank + p.rot_dim || q_abs.dtype != c.dtype || q_abs.rows != T ||
+        q_abs.cols != (int64_t)p.n_heads * c.head_dim ||
+        (p.rot_dim > 0 && (!q || q->dtype != c.dtype || q->rows != T || q->cols != (int64_t)p.n_heads * (p.qk_dim + p.rot_dim))) ||
+        (p.q_rank > 0 && (!q_latent || q_latent->dtype != c.dtype || q_latent->rows != T || q_latent->cols != p.q_rank)))
+        throw KernelError("latent_prepare: the projections, the queries and the one-plane cache disagree");
+    static auto fn = SANDY_KERNEL(latent_prepare, sandy_latent_prepare);
+    OpTimer timer(l, "latent norm + rotary + cache write", tensor_bytes(&down) + (double)T * c.head_dim * (p.n_heads + 1) * q_abs.elem_size(), 0);
+    check(fn((const float*)down.data, (int)down.ld, (int)T, p.q_rank, p.kv_rank, p.rot_dim, p.q_gain, p.kv_gain, p.eps, p.freq,
+             p.rot_dims, positions, token_seq, block_table, max_blocks, c.k, c.page_stride, c.page_size, c.num_pages, c.head_dim,
+             p.write_cache ? 1 : 0, q_latent ? q_latent->data : nullptr, q_latent ? (int)q_latent->ld : 0, q ? q->data : nullptr,
+             q ? (int)q->ld : 0, p.n_heads, p.qk_dim, q_abs.data, (int)q_abs.ld, code_of(c.dtype), l.kernel_status, l.stream),
+          "latent_prepare");
+}
+
+void head_product(const Launch& l, const Tensor& a, int a_gcols, const Tensor& w, int n_groups, Tensor& out, int o_gcols) {
+    if (n_groups <= 0 || w.rows % n_groups) throw KernelError("head_product: the weight's rows do not divide into the heads");
+    const int64_t N = w.rows / n_groups, K = w.cols;
+    if (a.dtype != w.dtype || a.rows != out.rows || a.cols < (int64_t)(n_groups - 1) * a_gcols + K ||
+        out.cols < (int64_t)(n_groups - 1) * o_gcols + N || (out.dtype != a.dtype && out.dtype != DType::F32))
+        throw KernelError("head_product: a " + dims(a) + ", w " + dims(w) + " and out " + dims(out) + " disagree");
+    if (left_out("product", N, K)) return;
+    static auto fn = SANDY_KERNEL(grouped_gemm, sandy_head_product);
+    OpTimer timer(l, "product per head (FFMA)", tensor_bytes(&w) + (double)a.rows * n_groups * (K * a.elem_size() + N * out.elem_size()),
+                  2.0 * a.rows * n_groups * N * K);
+    check(fn(a.data, (int)a.ld, a_gcols, w.data, (long long)N * w.ld, (int)w.ld, out.data, (int)out.ld, o_gcols, (int)a.rows, n_groups,
+             (int)N, (int)K, code_of(a.dtype), code_of(out.dtype), l.stream),
+          "head_product(G=" + std::to_string(n_groups) + ",N=" + std::to_string(N) + ",K=" + std::to_string(K) + ")");
+}
+
+void moe_route(const Launch& l, const Tensor& logits, const Tensor* bias, const Routing& r) {
+    if (logits.dtype != DType::F32 || logits.rows != r.n_tokens || logits.cols != r.n_experts ||
+        (bias && (bias->dtype != DType::F32 || bias->numel() != r.n_experts)))
+        throw KernelError("moe_route: float32 logits [tokens, experts] and a float32 bias [experts] expected");
+    static auto route = SANDY_KERNEL(moe, sandy_moe_route);
+    static auto group = SANDY_KERNEL(moe, sandy_moe_group);
+    {
+        OpTimer timer(l, "expert routing", tensor_bytes(&logits), 0);
+        check(route((const float*)logits.data, (int)logits.ld, bias ? (const float*)bias->data : nullptr, r.n_tokens, r.n_experts, r.top,
+                    r.expert_of, r.weight_of, l.stream),
+              "moe_route(E=" + std::to_string(r.n_experts) + ",top=" + std::to_string(r.top) + ")");
+    }
+    OpTimer timer(l, "expert grouping", 12.0 * r.n_tokens * r.top, 0);
+    check(group(r.expert_of, r.n_tokens * r.top, r.n_experts, r.group_start, r.entry_of_slot, r.slot_of_entry, l.stream), "moe_group");
+}
+
+void expert_product(const Launch& l, const Routing& r, const Tensor& a, bool gather, const Tensor& w, ExpertAct act, Tensor& out) {
+    if (r.n_experts <= 0 || w.rows % r.n_experts) throw KernelError("expert_product: the weight's rows do not divide into the experts");
+    const int64_t N = w.rows / r.n_experts, K = w.cols, slots = (int64_t)r.n_tokens * r.top;
+    if (a.dtype != w.dtype || a.cols != K || a.rows != (gather ? r.n_tokens : slots) || out.rows != slots || out.cols != N ||
+        (out.dtype != a.dtype && out.dtype != DType::F32))
+        throw KernelError("expert_product: a " + dims(a) + ", w " + dims(w) + " and out " + dims(out) + " disagree");
+    if (left_out("product", N, K)) return;
+    static auto fn = SANDY_KERNEL(grouped_gemm, sandy_expert_product);
+    // bytes: every expert's matrix at most once, and no more matrices than slots
+    const double matrices = std::min<double>(r.n_experts, (double)slots);
+    OpTimer timer(l, "product per expert (FFMA)", matrices * N * K * w.elem_size() + (double)slots * (K * a.elem_size() + N * out.elem_size()),
+                  2.0 * slots * N * K);
+    check(fn(a.data, (int)a.ld, w.data, (long long)N * w.ld, (int)w.ld, out.data, (int)out.ld, (int)slots, r.n_experts, (int)N, (int)K,
+             r.group_start, gather ? r.entry_of_slot : nullptr, gather ? r.top : 1, (int)act, code_of(a.dtype), code_of(out.dtype), l.stream),
+          "expert_product(E=" + std::to_string(r.n_experts) + ",N=" + std::to_string(N) + ",K=" + std::to_string(K) + ")");
+}
+
+void moe_combine(const Launch& l, const Routing& r, const Tensor& rows, Tensor& y, bool add) {
+    if (rows.dtype != DType::F32 || y.dtype != DType::F32 || rows.rows != (int64_t)r.n_tokens * r.top || y.rows != r.n_tokens ||
+        rows.cols != y.cols)
+        throw KernelError("moe_combine: float32 rows [tokens * top, width] and y [tokens, width] expected");
+    static auto fn = SANDY_KERNEL(moe, sandy_moe_combine);
+    OpTimer timer(l, "expert combine", tensor_bytes(&rows) + (add ? 2.0 : 1.0) * tensor_bytes(&y), 0);
+    check(fn((const float*)rows.data, (int)rows.ld, r.weight_of, r.slot_of_entry, r.n_tokens, r.top, (float*)y.data, (int)y.ld,
+             (int)y.cols, add ? 1 : 0, l.stream),
+          "moe_combine");
+}
+
 void attention_prepare(const Launch& l, const AttentionPrepare& p, const Tensor& proj, const KVView& c, const int* block_table,
                        int max_blocks, const int* token_seq, const int* positions, Tensor& q_out) {
     if (proj.dtype != c.dtype || q_out.dtype != proj.dtype || q_out.rows != proj.rows || q_out.cols != (int64_t)p.n_heads * c.head_dim ||

@@ -155,6 +155,52 @@ void glu(const Launch& l, const Tensor& a, const Tensor& b, GluAct act, Tensor& 
 // out = x rounded to out's type (out may be a column range of a wider matrix); x float32.
 void cast_cols(const Launch& l, const Tensor& x, Tensor& out);
 
+// x += gain * y (+ gain2 * y2): sublayer results joining the stream through a factor per channel; all float32.
+void scale_add(const Launch& l, const Tensor& y, const Tensor& gain, const Tensor* y2, const Tensor* gain2, Tensor& x);
+// x *= s, float32 (logits times a constant).
+void scale(const Launch& l, Tensor& x, float s);
+
+// ---- attention over a latent (latent_prepare.cu, grouped_gemm.cu) ---------------------------------------------
+// What the cache of such a layer holds per token, [latent | shared rotated key part | zeros], is key and value at
+// once (a one-plane page), and every query head becomes [U_k^T q | rotated part | zeros] of the same width.
+struct LatentPrepare {
+    int q_rank = 0;                    // > 0: queries pass a latent of their own; its norm is written to q_latent
+    int kv_rank = 0, rot_dim = 0;      // columns of `down`: q_rank, then kv_rank, then rot_dim
+    const float* q_gain = nullptr;     // float32 [q_rank]
+    const float* kv_gain = nullptr;    // float32 [kv_rank]
+    float eps = 0.0f;
+    const float* freq = nullptr;       // float32 [rot_dims / 2]; neighbours (2i, 2i+1) are a pair
+    int rot_dims = 0;                  // how many of the rot_dim entries turn
+    int n_heads = 0, qk_dim = 0;       // q is [T, n_heads * (qk_dim + rot_dim)]
+    bool write_cache = true;
+};
+// down float32 [T, q_rank + kv_rank + rot_dim]; q (read where rot_dim > 0) and q_abs [T, n_heads * cache.head_dim] of the
+// cache's dtype; q_latent [T, q_rank] of the cache's dtype or null.
+void latent_prepare(const Launch& l, const LatentPrepare& p, const Tensor& down, const Tensor* q, const KVView& cache,
+                    const int* block_table, int max_blocks, const int* token_seq, const int* positions, Tensor* q_latent,
+                    Tensor& q_abs);
+// out[t, g * o_gcols + n] = sum_k w[g][n][k] * a[t, g * a_gcols + k]: one small matrix per head.  w is [G * N, K].
+void head_product(const Launch& l, const Tensor& a, int a_gcols, const Tensor& w, int n_groups, Tensor& out, int o_gcols);
+
+// ---- mixture of experts (moe.cu, grouped_gemm.cu) ---------------------------------------------------------------
+// The routing of a step, all device data: entry t * top + j is the j-th choice of token t.
+struct Routing {
+    int n_tokens = 0, n_experts = 0, top = 0;
+    int* expert_of = nullptr;          // [n_tokens * top]
+    float* weight_of = nullptr;        // [n_tokens * top], softmax over a token's chosen logits
+    int* group_start = nullptr;        // [n_experts + 1] slots of every expert
+    int* entry_of_slot = nullptr;      // [n_tokens * top]
+    int* slot_of_entry = nullptr;      // [n_tokens * top]
+};
+// logits float32 [T, E] (+ bias float32 [E] or null) -> the routing's arrays.
+void moe_route(const Launch& l, const Tensor& logits, const Tensor* bias, const Routing& r);
+enum class ExpertAct : int { None = 0, ReluSquared = 1 };
+// out[s] = act(W_e a[row(s)]) for the slots s of every expert e; w [E * N, K]; with `gather` a slot reads its token's
+// row of `a` ([T, K]), else row s ([T * top, K]).  out [T * top, N].
+void expert_product(const Launch& l, const Routing& r, const Tensor& a, bool gather, const Tensor& w, ExpertAct act, Tensor& out);
+// y[t] (+)= sum_j weight[t, j] * rows[slot of (t, j)]; rows float32 [T * top, width], y float32 [T, width].
+void moe_combine(const Launch& l, const Routing& r, const Tensor& rows, Tensor& y, bool add);
+
 // ---- between a q/k/v projection and attention (attention_prepare.cu) -----------------------------------------
 struct AttentionPrepare {
     int n_heads = 0, n_kv_heads = 0, qk_dim = 0, v_dim = 0;       // the cache's head size is cache.head_dim >= both

@@ -204,14 +204,14 @@ private:
     DeviceWeight weight_;
 };
 
-// Output head: logits = y @ W^T in float32.  With `tied` the token table itself is the weight: the
+// Output head: logits = y @ W^T in float32, times `logit_scale` where a model has one.  With `tied` the token table itself is the weight: the
 // reference ties by naming `wte.weight` twice (:57, a transposed-operand matmul,
 // src/ir/MidIRPass.cpp:30-69), and no second copy exists here either.
 class OutputHead : public Head {
 public:
     explicit OutputHead(const PartSpec& s)
         : Head(s), vocab_(s.get_int("vocab_size")), width_(s.get_int("width")), tied_(s.get_bool("tied", false)),
-          linear_(width_, vocab_, false, "out_in", "head") {}
+          logit_scale_((float)s.get_double("logit_scale", 1.0)), linear_(width_, vocab_, false, "out_in", "head") {}
     TensorRequests requests() const override {
         if (tied_) return {};
         TensorRequest w;
@@ -232,10 +232,12 @@ public:
     size_t weight_bytes() const override { return linear_.weight_bytes(); }
     void forward(StepContext& ctx, const Tensor& y, Tensor& logits) override {
         linear_.run(ctx, nullptr, &y, logits, ops::Act::None, nullptr);
+        if (logit_scale_ != 1.0f) ops::scale(ctx.launch, logits, logit_scale_);      // on the float32 logits
     }
 private:
     int64_t vocab_, width_;
     bool tied_;
+    float logit_scale_;
     Linear linear_;
 };
 
@@ -404,7 +406,10 @@ Table& table() {
     static thread_local bool entered = false;
     if (!entered) {
         entered = true;
-        std::call_once(more, [] { register_hybrid_parts(); });
+        std::call_once(more, [] {
+            register_hybrid_parts();
+            register_latent_parts();
+        });
         entered = false;
     }
     return t;

@@ -103,6 +103,9 @@ public:
         (void)ctx; (void)y; (void)mult; (void)x;
         throw ConfigError("norm kind '" + spec_.kind + "' cannot follow a sublayer");
     }
+    // A part whose forward_add is x += mult * gain * y with one float32 factor per channel hands the factors out
+    // here, so that a block can join several branches to the stream in one pass.
+    virtual const Tensor* channel_gain() const { return nullptr; }
 };
 
 class PositionEncoding : public Part {
@@ -233,6 +236,9 @@ std::vector<std::string> part_kinds(const std::string& family);
 // Kinds of parts_hybrid.cpp: RMS norm, gated feed-forward, norms on both sides of a sublayer, attention with a sink
 // beside a matrix memory, the gated delta rule, the re-entry mix of a looped span.  Called once by the registry.
 void register_hybrid_parts();
+// Kinds of parts_latent.cpp: attention over a latent of keys and values, a routed mixture of experts, a factor per
+// channel behind a sublayer, the block whose two sublayers read one normed input.
+void register_latent_parts();
 
 template <typename T>
 std::unique_ptr<T> make_part(const std::string& family, const PartSpec& spec) {

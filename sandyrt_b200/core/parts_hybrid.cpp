@@ -20,10 +20,11 @@
 // (their values enter exponentials and recurrences).
 #include <cmath>
 
+#include "part_helpers.h"
 #include "parts.h"
 
 namespace sandy {
-namespace {
+namespace part_helpers {
 
 constexpr double kPi = 3.14159265358979323846;
 
@@ -55,7 +56,6 @@ HostTensor stack_rows(const std::vector<const HostTensor*>& parts, int64_t cols)
 
 // Columns of several [rows, n_i] matrices side by side; `pad_to[i]` widens part i with zero columns, and with
 // `group[i]` > 0 the padding goes behind every group of `group[i]` columns (heads padded to a larger head size).
-struct ColumnPart { const HostTensor* t; int64_t cols; int64_t group; int64_t group_padded; };
 HostTensor join_columns(const std::vector<ColumnPart>& parts, int64_t rows, int64_t total_cols) {
     auto buf = alloc_f32((size_t)(rows * total_cols));
     int64_t c0 = 0;
@@ -70,7 +70,7 @@ HostTensor join_columns(const std::vector<ColumnPart>& parts, int64_t rows, int6
     return host_f32(buf, {rows, total_cols});
 }
 
-TensorRequest want(std::vector<int64_t> shape, const char* init = "weight") {
+TensorRequest want(std::vector<int64_t> shape, const char* init) {
     TensorRequest r;
     r.shape = std::move(shape);
     r.init = init;
@@ -78,6 +78,42 @@ TensorRequest want(std::vector<int64_t> shape, const char* init = "weight") {
 }
 
 int64_t round_up(int64_t n, int64_t m) { return (n + m - 1) / m * m; }
+
+// ---- rotary frequencies ----------------------------------------------------------------------------------------
+// f_i = base^(-2i / dims), i < dims / 2.  With `scaling` {factor, low, high, original}: a frequency whose
+// wavelength 2 pi / f is shorter than original / high stays, longer than original / low is divided by factor,
+// and between the two is the blend (1 - s) f / factor + s f with s = (original / wavelength - low) / (high - low).
+std::vector<float> rotary_frequencies(int dims, double base, const Json* scaling) {
+    std::vector<float> out;
+    for (int i = 0; i < dims / 2; i++) {
+        double f = std::pow(base, -2.0 * i / dims);
+        if (scaling && scaling->is_object()) {
+            const double factor = scaling->at("factor").as_double(), low = scaling->at("low").as_double(),
+                         high = scaling->at("high").as_double(), orig = scaling->at("original").as_double();
+            const double wavelength = 2.0 * kPi / f;
+            if (wavelength < orig / high) {
+            } else if (wavelength > orig / low) {
+                f /= factor;
+            } else {
+                const double s = (orig / wavelength - low) / (high - low);
+                f = (1.0 - s) * f / factor + s * f;
+            }
+        }
+        out.push_back((float)f);
+    }
+    return out;
+}
+
+DeviceWeight floats_to_device(const std::vector<float>& v) {
+    auto buf = alloc_f32(v.size());
+    std::copy(v.begin(), v.end(), buf.get());
+    return to_device(host_f32(buf, {(int64_t)v.size()}), DType::F32);
+}
+
+}  // namespace part_helpers
+
+namespace {
+using namespace part_helpers;
 
 // ---- RMS norm --------------------------------------------------------------------------------------------
 // Parameters: width, eps.  Tensor: "weight" (a plain gain, not one-plus).
@@ -206,37 +242,6 @@ private:
     int64_t width_;
     Linear linear_;
 };
-
-// ---- rotary frequencies ----------------------------------------------------------------------------------------
-// f_i = base^(-2i / dims), i < dims / 2.  With `scaling` {factor, low, high, original}: a frequency whose
-// wavelength 2 pi / f is shorter than original / high stays, longer than original / low is divided by factor,
-// and between the two is the blend (1 - s) f / factor + s f with s = (original / wavelength - low) / (high - low).
-std::vector<float> rotary_frequencies(int dims, double base, const Json* scaling) {
-    std::vector<float> out;
-    for (int i = 0; i < dims / 2; i++) {
-        double f = std::pow(base, -2.0 * i / dims);
-        if (scaling && scaling->is_object()) {
-            const double factor = scaling->at("factor").as_double(), low = scaling->at("low").as_double(),
-                         high = scaling->at("high").as_double(), orig = scaling->at("original").as_double();
-            const double wavelength = 2.0 * kPi / f;
-            if (wavelength < orig / high) {
-            } else if (wavelength > orig / low) {
-                f /= factor;
-            } else {
-                const double s = (orig / wavelength - low) / (high - low);
-                f = (1.0 - s) * f / factor + s * f;
-            }
-        }
-        out.push_back((float)f);
-    }
-    return out;
-}
-
-DeviceWeight floats_to_device(const std::vector<float>& v) {
-    auto buf = alloc_f32(v.size());
-    std::copy(v.begin(), v.end(), buf.get());
-    return to_device(host_f32(buf, {(int64_t)v.size()}), DType::F32);
-}
 
 // ---- attention beside a matrix memory ----------------------------------------------------------------------------
 // Parameters: width, eps, left_scale, right_scale,

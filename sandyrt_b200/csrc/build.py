@@ -51,6 +51,9 @@ LIBRARIES: Dict[str, List[str]] = {
     "elementwise": [],
     "attention_prepare": [],
     "matrix_state": [],
+    "latent_prepare": [],
+    "grouped_gemm": [],
+    "moe": [],
 }
 
 

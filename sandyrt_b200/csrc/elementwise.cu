@@ -5,6 +5,9 @@
 //   sandy_cast_cols   out[t, c0 + j] = x[t, j]               float32 rows rounded into a column range of a wider matrix
 //                                                            of the compute type (the operand [x; x0] of a product
 //                                                            over two streams side by side)
+//   sandy_scale_add   x[t, j] += gain[j] * y[t, j]           a sublayer's result joins the stream through a learned
+//                                                            factor per channel (layer scale); all float32
+//   sandy_scale_f32   x[i] *= s                              float32 logits times a constant
 //
 // The activation is computed in 32-bit and the result rounded once.
 #include "common.cuh"
@@ -46,6 +49,26 @@ cast_cols_kernel(const float* __restrict__ x, int ldx, T* __restrict__ out, int 
     }
 }
 
+__global__ void __launch_bounds__(256)
+scale_add_kernel(const float* __restrict__ y, int ldy, const float* __restrict__ gain, const float* __restrict__ y2, int ldy2,
+                 const float* __restrict__ gain2, float* __restrict__ x, int ldx, int rows, int cols) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long long n = (long long)rows * cols;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / cols, j = i % cols;
+        float branch = gain[j] * y[t * ldy + j];
+        if (y2) branch += gain2[j] * y2[t * ldy2 + j];
+        x[t * ldx + j] += branch;
+    }
+}
+
+__global__ void __launch_bounds__(256) scale_f32_kernel(float* __restrict__ x, long long n, float s) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) x[i] *= s;
+}
+
 inline unsigned blocks_for(long long n) {
     const long long want = (n + 255) / 256;
     const long long cap = (long long)sandy_sm_count() * 16;
@@ -81,4 +104,20 @@ SANDY_API int sandy_cast_cols(const float* x, int ldx, void* out, int ld_out, in
     if (out_dtype == SANDY_BF16)
         return sandy_launch(cast_cols_kernel<bf16>, dim3(grid), dim3(256), 0, stream, x, ldx, (bf16*)out, ld_out, rows, cols);
     return SANDY_ERR_UNSUPPORTED;
+}
+
+// x [rows, cols] += gain [cols] * y [rows, cols] (+ gain2 * y2 where y2 is given: both branches of a layer whose
+// sublayers read the same input are added first, then joined to the stream); all float32.
+SANDY_API int sandy_scale_add(const float* y, int ldy, const float* gain, const float* y2, int ldy2, const float* gain2, float* x,
+                              int ldx, int rows, int cols, cudaStream_t stream) {
+    if (rows == 0 || cols == 0) return SANDY_OK;
+    if (!y || !gain || !x || (y2 && !gain2)) return SANDY_ERR_ARGUMENT;
+    return sandy_launch(scale_add_kernel, dim3(blocks_for((long long)rows * cols)), dim3(256), 0, stream, y, ldy, gain, y2, ldy2,
+                        gain2, x, ldx, rows, cols);
+}
+
+SANDY_API int sandy_scale_f32(float* x, long long n, float s, cudaStream_t stream) {
+    if (n == 0) return SANDY_OK;
+    if (!x) return SANDY_ERR_ARGUMENT;
+    return sandy_launch(scale_f32_kernel, dim3(blocks_for(n)), dim3(256), 0, stream, x, n, s);
 }

@@ -1,0 +1,134 @@
+// Routing of a mixture of experts, all on the device (a recorded step serves every routing):
+//
+//   sandy_moe_route    per token: logits z = router product + bias (32-bit); the `top` largest (ties: the lower
+//                      expert first) are chosen, their weights are the softmax over the chosen logits alone.
+//                      Entry t * top + j holds the j-th choice of token t.
+//   sandy_moe_group    entries sorted by expert: group_start[e] .. group_start[e+1]-1 are expert e's slots;
+//                      entry_of_slot and slot_of_entry are the two directions of the permutation.  Which slot of
+//                      its expert an entry gets is not fixed from run to run; nothing depends on it, since every
+//                      slot's row is computed on its own.
+//   sandy_moe_combine  y[t] (+)= sum_j weight[t, j] * rows[slot_of_entry[t * top + j]], in 32-bit, j in order.
+#include "common.cuh"
+
+namespace {
+
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ bias, int n_tokens, int n_experts,
+                 int top, int* __restrict__ expert_of, float* __restrict__ weight_of) {
+    extern __shared__ float z_all[];                 // [warps][n_experts]
+    pdl_wait();
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= n_tokens) return;
+    float* z = z_all + (size_t)warp * n_experts;
+    for (int e = lane; e < n_experts; e += 32) z[e] = logits[(size_t)t * ld + e] + (bias ? bias[e] : 0.0f);
+    __syncwarp();
+    float first = 0.0f, sum = 0.0f;
+    for (int j = 0; j < top; j++) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float v = z[e];
+            if (v > best) { best = v; arg = e; }     // ascending e: the first of equals stays
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (arg == 0x7fffffff) arg = j;              // every logit NaN or -inf: any expert, weight below is NaN or 0
+        if (j == 0) first = best;
+        const float w = expf(best - first);
+        sum += w;
+        if (lane == 0) {
+            expert_of[(size_t)t * top + j] = arg;
+            weight_of[(size_t)t * top + j] = w;
+            z[arg] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    if (lane < top) weight_of[(size_t)t * top + lane] /= sum;      // top <= 32; lane 0's writes are visible after the syncwarp
+}
+
+__global__ void __launch_bounds__(1024)
+moe_group_kernel(const int* __restrict__ expert_of, int n_entries, int n_experts, int* __restrict__ group_start,
+                 int* __restrict__ entry_of_slot, int* __restrict__ slot_of_entry) {
+    extern __shared__ int counts[];                  // [n_experts] counts, then [n_experts] cursors
+    int* cursor = counts + n_experts;
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_entries; i += blockDim.x) {
+        const int e = expert_of[i];
+        if (e >= 0 && e < n_experts) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < n_experts; e++) {
+            group_start[e] = at;
+            cursor[e] = at;
+            at += counts[e];
+        }
+        group_start[n_experts] = at;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_entries; i += blockDim.x) {
+        const int e = expert_of[i];
+        if (e < 0 || e >= n_experts) continue;
+        const int s = atomicAdd(&cursor[e], 1);
+        entry_of_slot[s] = i;
+        slot_of_entry[i] = s;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ rows, int ld_rows, const float* __restrict__ weight_of,
+                   const int* __restrict__ slot_of_entry, int top, float* __restrict__ y, int ldy, int width, int add) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float acc = 0.0f;
+        for (int j = 0; j < top; j++) {
+            const int s = slot_of_entry[(size_t)t * top + j];
+            acc = fmaf(weight_of[(size_t)t * top + j], rows[(size_t)s * ld_rows + c], acc);
+        }
+        float* dst = y + (size_t)t * ldy + c;
+        *dst = add ? *dst + acc : acc;
+    }
+}
+
+}  // namespace
+
+// logits: float32 [n_tokens, >= n_experts] with pitch ld; bias float32 [n_experts] or null; 1 <= top <= min(32, n_experts).
+SANDY_API int sandy_moe_route(const float* logits, int ld, const float* bias, int n_tokens, int n_experts, int top,
+                              int* expert_of, float* weight_of, cudaStream_t stream) {
+    if (n_tokens == 0) return SANDY_OK;
+    if (!logits || !expert_of || !weight_of) return SANDY_ERR_ARGUMENT;
+    if (top < 1 || top > 32 || top > n_experts || n_experts > 2048) return SANDY_ERR_UNSUPPORTED;
+    const int warps = 4;
+    return sandy_launch(moe_route_kernel, dim3((n_tokens + warps - 1) / warps), dim3(32 * warps),
+                        (size_t)warps * n_experts * sizeof(float), stream, logits, ld, bias, n_tokens, n_experts, top, expert_of,
+                        weight_of);
+}
+
+SANDY_API int sandy_moe_group(const int* expert_of, int n_entries, int n_experts, int* group_start, int* entry_of_slot,
+                              int* slot_of_entry, cudaStream_t stream) {
+    if (!expert_of || !group_start || !entry_of_slot || !slot_of_entry) return SANDY_ERR_ARGUMENT;
+    if (n_experts < 1 || n_experts > 4096) return SANDY_ERR_UNSUPPORTED;
+    return sandy_launch(moe_group_kernel, dim3(1), dim3(1024), (size_t)2 * n_experts * sizeof(int), stream, expert_of,
+                        n_entries, n_experts, group_start, entry_of_slot, slot_of_entry);
+}
+
+// rows: float32 [n_tokens * top, width] by slot; y: float32 [n_tokens, width]; add != 0 adds to y, else writes it.
+SANDY_API int sandy_moe_combine(const float* rows, int ld_rows, const float* weight_of, const int* slot_of_entry, int n_tokens,
+                                int top, float* y, int ldy, int width, int add, cudaStream_t stream) {
+    if (n_tokens == 0 || width == 0) return SANDY_OK;
+    if (!rows || !weight_of || !slot_of_entry || !y) return SANDY_ERR_ARGUMENT;
+    return sandy_launch(moe_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, rows, ld_rows, weight_of, slot_of_entry, top,
+                        y, ldy, width, add);
+}

@@ -161,6 +161,31 @@ int sandy_head_norm_gate(const float* o, int ldo, const float* gain, int gain_st
 int sandy_glu(const void* a, const void* b, int ld_in, void* out, int ld_out, int rows, int cols, int act, int dtype,
               cudaStream_t stream);
 int sandy_cast_cols(const float* x, int ldx, void* out, int ld_out, int rows, int cols, int out_dtype, cudaStream_t stream);
+int sandy_scale_add(const float* y, int ldy, const float* gain, const float* y2, int ldy2, const float* gain2, float* x, int ldx,
+                    int rows, int cols, cudaStream_t stream);
+int sandy_scale_f32(float* x, long long n, float s, cudaStream_t stream);
+
+/* latent_prepare.cu */
+int sandy_latent_prepare(const float* down, int ld_down, int n_tokens, int q_rank, int kv_rank, int rot_dim, const float* q_gain,
+                         const float* kv_gain, float eps, const float* freq, int rot_dims, const int* positions,
+                         const int* token_seq, const int* block_table, int max_blocks, void* cache, long long page_stride,
+                         int page_size, int num_pages, int pad_dim, int write_cache, void* q_latent, int ld_ql, const void* q,
+                         int ld_q, int n_heads, int qk_dim, void* q_abs, int ld_qa, int dtype, int* status, cudaStream_t stream);
+
+/* grouped_gemm.cu */
+int sandy_head_product(const void* a, int lda, int a_gcols, const void* w, long long w_gstride, int ldw, void* out, int ldo,
+                       int o_gcols, int rows, int n_groups, int N, int K, int in_dtype, int out_dtype, cudaStream_t stream);
+int sandy_expert_product(const void* a, int lda, const void* w, long long w_gstride, int ldw, void* out, int ldo, int n_slots,
+                         int n_groups, int N, int K, const int* group_start, const int* a_row, int a_row_div, int act,
+                         int in_dtype, int out_dtype, cudaStream_t stream);
+
+/* moe.cu */
+int sandy_moe_route(const float* logits, int ld, const float* bias, int n_tokens, int n_experts, int top, int* expert_of,
+                    float* weight_of, cudaStream_t stream);
+int sandy_moe_group(const int* expert_of, int n_entries, int n_experts, int* group_start, int* entry_of_slot, int* slot_of_entry,
+                    cudaStream_t stream);
+int sandy_moe_combine(const float* rows, int ld_rows, const float* weight_of, const int* slot_of_entry, int n_tokens, int top,
+                      float* y, int ldy, int width, int add, cudaStream_t stream);
 
 /* matrix_state.cu */
 long long sandy_mlstm_state_floats(int n_heads, int qk_dim, int v_dim);

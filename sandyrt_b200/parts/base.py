@@ -41,9 +41,11 @@ class PagedKVSpec:
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None   # None: all positions stay; n: only the last n are read
+    planes: int = 2                # 1: a page holds one plane and a view's values are its keys (a latent that is both)
 
     def to_json(self) -> Dict[str, Any]:
-        return {"kind": "paged", "n_kv_heads": self.n_kv_heads, "head_dim": self.head_dim, "window": self.window or 0}
+        return {"kind": "paged", "n_kv_heads": self.n_kv_heads, "head_dim": self.head_dim, "window": self.window or 0,
+                "planes": self.planes}
 
 
 @dataclasses.dataclass(frozen=True)

@@ -40,8 +40,10 @@ _KEEP: List[Any] = []            # callbacks and strings the library holds point
 def _builtin_config_classes() -> Dict[str, Type[ModelConfig]]:
     from .config.gpt2 import GPT2Config
     from .config.panupel import PanupelConfig
+    from .config.sovezen import SovezenConfig
 
-    return {GPT2Config.architecture: GPT2Config, PanupelConfig.architecture: PanupelConfig}
+    return {GPT2Config.architecture: GPT2Config, PanupelConfig.architecture: PanupelConfig,
+            SovezenConfig.architecture: SovezenConfig}
 
 
 def _text(s: str) -> int:
