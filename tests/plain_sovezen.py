@@ -177,6 +177,36 @@ def forward(cfg: dict, w: Weights, tokens: List[int], dtype=torch.float64, strea
     return linear(w["embed"], y, keep32=True) * cfg["logit_scale"]
 
 
+def forward_rounded(cfg: dict, w: Weights, tokens: List[int]) -> torch.Tensor:
+    """The same with every product's operands and results rounded to bfloat16 values."""
+    global ROUND_PRODUCTS
+    ROUND_PRODUCTS = True
+    try:
+        return forward(cfg, w, tokens)
+    finally:
+        ROUND_PRODUCTS = False
+
+
+def router_margin(cfg: dict, w: Weights, tokens: List[int]) -> float:
+    """How close the closest call of any router is on this sequence: the smallest gap between the last logit chosen
+    and the first one left out, over the spread of that router's logits."""
+    w64 = {k: (v.to(torch.float64) if v.is_floating_point() else v) for k, v in w.items()}
+    x = w64["embed"][torch.tensor(tokens, dtype=torch.long)]
+    positions = torch.arange(len(tokens))
+    worst = math.inf
+    for i, spec in enumerate(cfg["layers"]):
+        mlp = spec.get("mlp")
+        if mlp is not None and mlp["kind"] == "moe" and mlp["router"]["top"] < mlp["router"]["experts"]:
+            pre = f"l{spec.get('weights_of', i)}."
+            h = rms_norm(x, w64[pre + "norm1"], cfg["norm"]["eps"])
+            z = linear(w64[pre + "mlp.router"], h) + w64[pre + "mlp.router.b"]
+            s = z.sort(-1, descending=True).values
+            top = mlp["router"]["top"]
+            worst = min(worst, float(((s[:, top - 1] - s[:, top]) / z.std()).min()))
+        x = layer(cfg, w64, i, x, positions)
+    return worst
+
+
 def greedy(cfg: dict, w: Weights, prompt: List[int], n: int) -> List[int]:
     toks = list(prompt)
     for _ in range(n):
