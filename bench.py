@@ -5,6 +5,7 @@
     python bench.py --profile-kernels             time per kernel class of a decode and a prompt step
     python bench.py --attribute [--batch B]       what each family of launches costs inside a step (leave-one-out)
     python bench.py --hybrid [--batch B]          Panupel beside GPT-2 at equal layer sizes: throughput, time per kernel class
+    python bench.py --latent [--batch B]          Sovezen beside GPT-2 at equal layer sizes, likewise
     python bench.py --micro gemm|decode-attention|prefill-attention [...]   kernel micro-benchmarks
 
 Default workload: GPT-2 small (12 layers, width 768, 12 heads of 64, inner 3072, vocabulary 50257,
@@ -436,10 +437,30 @@ def hybrid_config(width, heads, kv_heads, ff, vocab=50257, layers=4):
             "layers": [delta if i % 2 == 0 else par for i in range(layers)]}
 
 
-def hybrid(dtype_name: str, layers: int, batch: int, steps: int, warmup: int) -> int:
-    """Prefill and decode throughput of Panupel at sizes that resemble real layers, beside GPT-2 with the same width,
-    heads, layer count and vocabulary, both with random weights; then the device time per kernel class of both, so
-    that like kernels can be held against each other.  One JSON line per size, then the tables."""
+# ---- attention over a latent (Sovezen) beside GPT-2 at equal size --------------------------------------------
+# Heads of 64 plus 32 rotated entries, a latent of 96 (cache rows of 96 + 32 = 128, the widest row that the prompt
+# attention's tensor-core kernel and every decode kernel take), a query latent of half the width; the routed
+# feed-forward has 16 experts of which 2 run, each half as wide as the dense one, so both move the same weights a token.
+LATENT_SIZES = HYBRID_SIZES
+
+
+def latent_config(width, heads, kv_heads, ff, vocab=50257, layers=4):
+    del kv_heads
+    rot = {"type": "latent_attention", "mixer": {"heads": heads, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 96,
+                                                 "scale": 96 ** -0.5, "rot": {"dims": 32, "base": 10000.0}}}
+    lat = {"type": "latent_attention_2", "mixer": {"heads": heads, "dim": 64, "vdim": 64, "kv_rank": 128, "q_rank": width // 2,
+                                                   "scale": 0.125}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": ff // 2}, "router": {"experts": 16, "top": 2}}
+    order = [(rot, dense), (lat, moe), (lat, dense), (rot, moe)]
+    return {"architecture": "Sovezen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
+            "layers": [{**order[i % 4][0], "mlp": order[i % 4][1]} for i in range(layers)]}
+
+
+def hybrid(dtype_name: str, layers: int, batch: int, steps: int, warmup: int, design: str = "panupel") -> int:
+    """Prefill and decode throughput of a design (Panupel or Sovezen) at sizes that resemble real layers, beside GPT-2
+    with the same width, heads, layer count and vocabulary, both with random weights; then the device time per kernel
+    class of both, so that like kernels can be held against each other.  One JSON line per size, then the tables."""
     import numpy as np
     import torch
 
@@ -450,10 +471,11 @@ def hybrid(dtype_name: str, layers: int, batch: int, steps: int, warmup: int) ->
     peaks = load_peaks()
     layers = layers or 4
     rng = np.random.default_rng(0)
+    hybrid_config = {"panupel": globals()["hybrid_config"], "sovezen": latent_config}[design]
     for name, sz in HYBRID_SIZES.items():
         gpt2_raw = {**load_model_config("small"), "n_embd": sz["width"], "n_head": sz["heads"], "n_inner": None, "n_layer": layers}
         out = {"size": name, "layers": layers, "dtype": dtype_name, "data": "synthetic", "peaks": peaks["source"]}
-        for arch, raw in (("panupel", hybrid_config(layers=layers, **sz)), ("gpt2", gpt2_raw)):
+        for arch, raw in ((design, hybrid_config(layers=layers, **sz)), ("gpt2", gpt2_raw)):
             cfg = config_from_normalised(raw)
             cfg.validate()
             model = build_model(cfg)
@@ -475,7 +497,7 @@ def hybrid(dtype_name: str, layers: int, batch: int, steps: int, warmup: int) ->
     # per kernel class, eager launches with events around each
     for name, sz in HYBRID_SIZES.items():
         gpt2_raw = {**load_model_config("small"), "n_embd": sz["width"], "n_head": sz["heads"], "n_inner": None, "n_layer": layers}
-        for arch, raw in (("panupel", hybrid_config(layers=layers, **sz)), ("gpt2", gpt2_raw)):
+        for arch, raw in ((design, hybrid_config(layers=layers, **sz)), ("gpt2", gpt2_raw)):
             print(f"---- {arch}, width {name} ----")
             kernel_table(config_from_normalised(raw), dtype_name, batch)
     return 0
@@ -501,6 +523,8 @@ def main() -> int:
     ap.add_argument("--attribute-prompts", default="2x1024", help="the prompt step of --attribute: requests x tokens")
     ap.add_argument("--hybrid", action="store_true",
                     help="Panupel beside GPT-2 at equal sizes: decode and prefill throughput, then time per kernel class")
+    ap.add_argument("--latent", action="store_true",
+                    help="Sovezen (attention over a latent, routed experts) beside GPT-2 at equal sizes, as --hybrid does for Panupel")
     ap.add_argument("--micro", nargs=argparse.REMAINDER, help="run a kernel micro-benchmark (see sandyrt_b200/csrc/microbench.py)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -511,8 +535,9 @@ def main() -> int:
     if args.micro is not None:
         from sandyrt_b200.csrc import microbench
         return microbench.main(args.micro)
-    if args.hybrid:
-        return hybrid(args.dtype, args.layers, args.batch, min(args.steps, 128), args.warmup)
+    if args.hybrid or args.latent:
+        return hybrid(args.dtype, args.layers, args.batch, min(args.steps, 128), args.warmup,
+                      design="sovezen" if args.latent else "panupel")
     if args.workload:
         return workload(args.workload, args.dtype, args.layers)
     if args.profile_kernels:
