@@ -7,14 +7,16 @@
 //                slots group_start[g] .. group_start[g+1]-1 belong to expert g (device data: the routing of this
 //                step), a slot reads the row a_row[s] / a_row_div of `a` (or row s) and writes row s of `out`
 //
-// One kernel serves both: a block computes a 32 x 64 tile of one group's output, operands staged through shared
-// memory as floats 32 k at a time, every sum carried in 32-bit in a fixed order of k (so a row's result does not
-// depend on which rows share its tile).  The weight is [N, K] row-major per group.  A grid of the per-expert form
-// covers the worst case of tiles (slots / 32 + groups) and blocks beyond the step's tiles leave at once, so a
-// recorded launch serves every routing.
+// Both forms share their kernels: a block computes one tile of one group's output, every sum carried in 32-bit in
+// a fixed order of k (so a row's result does not depend on which rows share its tile).  The weight is [N, K]
+// row-major per group.  A grid of the per-expert form covers the worst case of tiles (slots / tile rows + groups)
+// and blocks beyond the step's tiles leave at once, so a recorded launch serves every routing.
 //
-// These are FFMA tiles, not tensor-core tiles: K and N here are a head's or an expert's sizes (tens to a few
-// hundred), and both compute types share the code.
+// Two kernels.  bfloat16 operands whose rows start on 16-byte boundaries go through tensor cores (mma.sync
+// m16n8k16, 64 x 64 tiles, operands staged by cp.async in a ring of four stages and read with ldmatrix; rows a tile
+// does not have are zero-filled, so a decode step's one or two rows per expert cost a tile's weight traffic and
+// nothing else).  float32 operands and odd sizes take FFMA tiles.  Which kernel runs is a matter of the model's
+// sizes alone, never of a step's rows.
 #include "common.cuh"
 
 namespace {
@@ -118,12 +120,155 @@ __global__ void __launch_bounds__(THREADS) grouped_tile_kernel(GroupedArgs p) {
     }
 }
 
+// ---- tensor-core tiles (bfloat16) ---------------------------------------------------------------------------------
+constexpr int MM = 64, MN = 64, MK = 32, MSTAGES = 4, MPITCH = MK + 8, MTHREADS = 128;
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;               // 0: nothing is read and the 16 bytes become zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(MTHREADS) grouped_mma_kernel(GroupedArgs p) {
+    __shared__ __align__(16) bf16 sA[MSTAGES][MM][MPITCH];
+    __shared__ __align__(16) bf16 sB[MSTAGES][MN][MPITCH];
+    __shared__ int s_rows[MM];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int tid = threadIdx.x;
+    int g, row0, row_end;
+    if (p.group_start) {
+        int tile = blockIdx.y;
+        g = 0;
+        int start = p.group_start[0], end = start;
+        for (; g < p.G; g++) {
+            end = p.group_start[g + 1];
+            const int tiles = (end - start + MM - 1) / MM;
+            if (tile < tiles) break;
+            tile -= tiles;
+            start = end;
+        }
+        if (g >= p.G) return;
+        row0 = start + tile * MM;
+        row_end = end;
+    } else {
+        g = blockIdx.z;
+        row0 = blockIdx.y * MM;
+        row_end = p.rows;
+    }
+    const int n0 = blockIdx.x * MN;
+    if (tid < MM) {
+        const int s = row0 + tid;
+        int r = -1;
+        if (s < row_end) r = p.a_row ? p.a_row[s] / p.a_row_div : s;
+        s_rows[tid] = r;
+    }
+    __syncthreads();
+    const bf16* A = (const bf16*)p.a + (size_t)g * p.a_gcols;
+    const bf16* W = (const bf16*)p.w + (size_t)g * p.w_gstride;
+    // a stage: 64 rows x 4 pieces of 8 for each operand; a thread copies two pieces of each
+    auto load_stage = [&](int stage, int k0) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int c = tid + i * MTHREADS, r = c >> 2, kc = (c & 3) * 8;
+            const int ar = s_rows[r];
+            const bool va = ar >= 0 && k0 + kc < p.K;
+            cp_async_16(&sA[stage][r][kc], va ? (const void*)(A + (size_t)ar * p.lda + k0 + kc) : (const void*)A, va);
+            const int n = n0 + r;
+            const bool vb = n < p.N && k0 + kc < p.K;
+            cp_async_16(&sB[stage][r][kc], vb ? (const void*)(W + (size_t)n * p.ldw + k0 + kc) : (const void*)W, vb);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int n_k = (p.K + MK - 1) / MK;
+#pragma unroll
+    for (int s = 0; s < MSTAGES - 1; s++) {
+        if (s < n_k) load_stage(s, s * MK);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    const int warp = tid >> 5, lane = tid & 31;
+    const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+    float acc[2][4][4] = {};
+    for (int kt = 0; kt < n_k; kt++) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(MSTAGES - 2) : "memory");
+        __syncthreads();                             // stage kt has landed for everyone, stage kt - 1 has been read by everyone
+        if (kt + MSTAGES - 1 < n_k) load_stage((kt + MSTAGES - 1) % MSTAGES, (kt + MSTAGES - 1) * MK);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+        const int st = kt % MSTAGES;
+#pragma unroll
+        for (int kk = 0; kk < MK; kk += 16) {
+            unsigned a[2][4], b[2][4];
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++)
+                ldmatrix_x4(a[mt], &sA[st][wm + mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][kk + (lane >> 4) * 8]);
+#pragma unroll
+            for (int np = 0; np < 2; np++)
+                ldmatrix_x4(b[np], &sB[st][wn + np * 16 + (lane & 7) + (lane >> 4) * 8][kk + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+                for (int nt = 0; nt < 4; nt++) mma_bf16(acc[mt][nt], a[mt], b[nt >> 1][(nt & 1) * 2], b[nt >> 1][(nt & 1) * 2 + 1]);
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    TO* O = (TO*)p.out + (size_t)g * p.o_gcols;
+    const int gq = lane >> 2, tq = lane & 3;
+#pragma unroll
+    for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            const int s = row0 + wm + mt * 16 + gq + half * 8;
+            if (s >= row_end) continue;
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++)
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    const int n = n0 + wn + nt * 8 + tq * 2 + j;
+                    if (n >= p.N) continue;
+                    float v = acc[mt][nt][half * 2 + j];
+                    if (p.act == 1) {
+                        v = fmaxf(v, 0.0f);
+                        v = v * v;
+                    }
+                    O[(size_t)s * p.ldo + n] = from_f32<TO>(v);
+                }
+        }
+}
+
+// Whether the tensor-core kernel can take a problem: every row piece a cp.async fetches starts on a 16-byte boundary.
+bool mma_takes(const GroupedArgs& p) {
+    return p.K % 8 == 0 && p.lda % 8 == 0 && p.ldw % 8 == 0 && p.a_gcols % 8 == 0 && p.w_gstride % 8 == 0 &&
+           !((uintptr_t)p.a & 15) && !((uintptr_t)p.w & 15);
+}
+
 template <typename TA, typename TO>
 int launch(const GroupedArgs& p, dim3 grid, cudaStream_t stream) {
     return sandy_launch(grouped_tile_kernel<TA, TO>, grid, dim3(THREADS), 0, stream, p);
 }
 
-int dispatch(const GroupedArgs& p, dim3 grid, int in_dtype, int out_dtype, cudaStream_t stream) {
+// `row_tiles(tile rows)` gives the grid's second dimension for a kernel's tile height.
+template <typename F>
+int dispatch(const GroupedArgs& p, F row_tiles, int groups_z, int in_dtype, int out_dtype, cudaStream_t stream) {
+    if (in_dtype == SANDY_BF16 && mma_takes(p)) {
+        const dim3 grid((p.N + MN - 1) / MN, row_tiles(MM), groups_z);
+        if (grid.y > 65535) return SANDY_ERR_UNSUPPORTED;
+        if (out_dtype == SANDY_BF16) return sandy_launch(grouped_mma_kernel<bf16>, grid, dim3(MTHREADS), 0, stream, p);
+        if (out_dtype == SANDY_F32) return sandy_launch(grouped_mma_kernel<float>, grid, dim3(MTHREADS), 0, stream, p);
+        return SANDY_ERR_UNSUPPORTED;
+    }
+    const dim3 grid((p.N + TN - 1) / TN, row_tiles(TM), groups_z);
+    if (grid.y > 65535) return SANDY_ERR_UNSUPPORTED;
     if (in_dtype == SANDY_F32 && out_dtype == SANDY_F32) return launch<float, float>(p, grid, stream);
     if (in_dtype == SANDY_BF16 && out_dtype == SANDY_BF16) return launch<bf16, bf16>(p, grid, stream);
     if (in_dtype == SANDY_BF16 && out_dtype == SANDY_F32) return launch<bf16, float>(p, grid, stream);
@@ -139,9 +284,9 @@ SANDY_API int sandy_head_product(const void* a, int lda, int a_gcols, const void
                                  cudaStream_t stream) {
     if (rows == 0 || n_groups == 0 || N == 0) return SANDY_OK;
     if (!a || !w || !out) return SANDY_ERR_ARGUMENT;
-    if (n_groups > 65535 || (rows + TM - 1) / TM > 65535) return SANDY_ERR_UNSUPPORTED;
+    if (n_groups > 65535) return SANDY_ERR_UNSUPPORTED;
     GroupedArgs p = {a, lda, a_gcols, w, w_gstride, ldw, out, ldo, o_gcols, N, K, n_groups, rows, nullptr, nullptr, 1, 0};
-    return dispatch(p, dim3((N + TN - 1) / TN, (rows + TM - 1) / TM, n_groups), in_dtype, out_dtype, stream);
+    return dispatch(p, [&](int tile) { return (rows + tile - 1) / tile; }, n_groups, in_dtype, out_dtype, stream);
 }
 
 // Per expert: `n_slots` bounds the slots (tokens x experts per token); group_start int32 [G + 1] on the device; a_row
@@ -151,8 +296,7 @@ SANDY_API int sandy_expert_product(const void* a, int lda, const void* w, long l
                                    int a_row_div, int act, int in_dtype, int out_dtype, cudaStream_t stream) {
     if (n_slots == 0 || n_groups == 0 || N == 0) return SANDY_OK;
     if (!a || !w || !out || !group_start || a_row_div < 1) return SANDY_ERR_ARGUMENT;
-    const int tiles = (n_slots + TM - 1) / TM + n_groups;
-    if (tiles > 65535) return SANDY_ERR_UNSUPPORTED;
     GroupedArgs p = {a, lda, 0, w, w_gstride, ldw, out, ldo, 0, N, K, n_groups, 0, group_start, a_row, a_row_div, act};
-    return dispatch(p, dim3((N + TN - 1) / TN, tiles, 1), in_dtype, out_dtype, stream);
+    // the worst case of tiles: every group's last tile partly filled
+    return dispatch(p, [&](int tile) { return (n_slots + tile - 1) / tile + n_groups; }, 1, in_dtype, out_dtype, stream);
 }
