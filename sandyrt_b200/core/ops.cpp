@@ -482,7 +482,7 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
     const float* sk = extras ? extras->sink : nullptr;
     const float* og = extras ? extras->out_gate : nullptr;
     const int d = c.head_dim, hkv = c.n_kv_heads;
-    if (d % 16 != 0 || d > 256) throw UnsupportedShape("attention: head size " + std::to_string(d) + " must be a multiple of 16, at most 256");
+    if (d % 16 != 0 || d > kMaxHeadDim) throw UnsupportedShape("attention: head size " + std::to_string(d) + " must be a multiple of 16, at most " + std::to_string(kMaxHeadDim));
     if (hkv <= 0 || n_heads % hkv != 0)
         throw UnsupportedShape("attention: " + std::to_string(n_heads) + " heads do not divide into " + std::to_string(hkv) + " key/value heads");
     if (q.cols != (int64_t)n_heads * d || out.rows != q.rows || out.cols != q.cols || q.dtype != c.dtype || out.dtype != q.dtype)
@@ -670,7 +670,7 @@ void head_product(const Launch& l, const Tensor& a, int a_gcols, const Tensor& w
         throw KernelError("head_product: a " + dims(a) + ", w " + dims(w) + " and out " + dims(out) + " disagree");
     if (left_out("product", N, K)) return;
     static auto fn = SANDY_KERNEL(grouped_gemm, sandy_head_product);
-    OpTimer timer(l, "product per head (FFMA)", tensor_bytes(&w) + (double)a.rows * n_groups * (K * a.elem_size() + N * out.elem_size()),
+    OpTimer timer(l, "product per head", tensor_bytes(&w) + (double)a.rows * n_groups * (K * a.elem_size() + N * out.elem_size()),
                   2.0 * a.rows * n_groups * N * K);
     check(fn(a.data, (int)a.ld, a_gcols, w.data, (long long)N * w.ld, (int)w.ld, out.data, (int)out.ld, o_gcols, (int)a.rows, n_groups,
              (int)N, (int)K, code_of(a.dtype), code_of(out.dtype), l.stream),
@@ -703,7 +703,7 @@ void expert_product(const Launch& l, const Routing& r, const Tensor& a, bool gat
     static auto fn = SANDY_KERNEL(grouped_gemm, sandy_expert_product);
     // bytes: every expert's matrix at most once, and no more matrices than slots
     const double matrices = std::min<double>(r.n_experts, (double)slots);
-    OpTimer timer(l, "product per expert (FFMA)", matrices * N * K * w.elem_size() + (double)slots * (K * a.elem_size() + N * out.elem_size()),
+    OpTimer timer(l, "product per expert", matrices * N * K * w.elem_size() + (double)slots * (K * a.elem_size() + N * out.elem_size()),
                   2.0 * slots * N * K);
     check(fn(a.data, (int)a.ld, w.data, (long long)N * w.ld, (int)w.ld, out.data, (int)out.ld, (int)slots, r.n_experts, (int)N, (int)K,
              r.group_start, gather ? r.entry_of_slot : nullptr, gather ? r.top : 1, (int)act, code_of(a.dtype), code_of(out.dtype), l.stream),

@@ -134,6 +134,9 @@ struct AttentionExtras {
     const float* sink = nullptr;
     const float* out_gate = nullptr;
 };
+// The widest head any attention kernel takes (the general kernel; the tensor-core prompt kernels take up to 128, the
+// decode kernels 16 / 32 / 64 / 128 and, in bfloat16, 256).
+constexpr int kMaxHeadDim = 640;
 // Attention of a step's tokens over the cache: picks the kernel for the step's shape.
 void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const KVView& cache, Tensor& out, int n_heads,
                float scale, int window, Workspace& ws, const AttentionExtras* extras = nullptr);

@@ -43,7 +43,8 @@ public:
           q_(q_rank_ ? q_rank_ : width_, (int64_t)H_ * (d_ + r_), false, "out_in", "q"),
           out_((int64_t)H_ * e_, width_, false, "out_in", "out") {
         if (H_ <= 0 || d_ <= 0 || e_ <= 0 || c_ <= 0 || r_ < 0 || q_rank_ < 0) throw ConfigError("latent_attention: sizes must be positive");
-        if (pad_ > 256) throw ConfigError("latent_attention: kv_rank + rot_dim is at most 256, got " + std::to_string(c_ + r_));
+        if (pad_ > ops::kMaxHeadDim)
+            throw ConfigError("latent_attention: kv_rank + rot_dim is at most " + std::to_string(ops::kMaxHeadDim) + ", got " + std::to_string(c_ + r_));
         if (rot_dims_ < 0 || rot_dims_ > r_ || rot_dims_ % 2) throw ConfigError("latent_attention: rot_dims must be even and at most rot_dim");
         if (q_rank_ && r_) throw ConfigError("latent_attention: a query latent and a rotated part together are not supported");
         const std::string pairs = s.get_string("rot_pairs", "neighbours");

@@ -213,7 +213,7 @@ void SovezenConfig::validate() const {
         } else {
             positive(l.q_rank, at, "q_rank");
         }
-        if (l.kv_rank + l.rot_dim > 256) bad(at, "kv_rank + rot_dim is at most 256 (the attention kernels' widest head)");
+        if (l.kv_rank + l.rot_dim > 640) bad(at, "kv_rank + rot_dim is at most 640 (the attention kernels' widest head)");
         if (l.mlp == "dense") positive(l.ff, at + ".mlp", "ff");
         if (l.mlp == "moe") {
             positive(l.ff, at + ".mlp.expert", "ff");

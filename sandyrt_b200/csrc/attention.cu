@@ -20,13 +20,15 @@
 // Cache layout of one layer: K and V each [num_pages][Hkv][page_size][D], page stride
 // given in elements (K and V of a page may be interleaved in one arena).
 //
-// This is the general kernel: any head size that is a multiple of 16 up to 256, any
-// number of heads and groups, both storage types.  One warp owns one (token, head) pair.
+// This is the general kernel: any head size that is a multiple of 16 up to 640 (two instantiations: up to
+// 256, and beyond for the wide rows of attention over a latent), any number of heads and groups, both
+// storage types.  One warp owns one (token, head) pair.
 #include "common.cuh"
 
 namespace {
 
-constexpr int MAX_HEAD_DIM = 256;
+constexpr int MAX_HEAD_DIM = 256;            // the common instantiation
+constexpr int WIDE_HEAD_DIM = 640;           // the other
 constexpr int WARPS_PER_BLOCK = 4;
 
 template <typename T>
@@ -90,7 +92,7 @@ __device__ __forceinline__ float dot_row<bf16>(const bf16* __restrict__ row, con
     return acc;
 }
 
-template <typename T>
+template <typename T, int MAX_D>
 __global__ void __launch_bounds__(WARPS_PER_BLOCK * 32)
 paged_attention_kernel(const T* __restrict__ q, int ld_q,
                        const T* __restrict__ k_cache, const T* __restrict__ v_cache, long long page_stride,
@@ -100,7 +102,7 @@ paged_attention_kernel(const T* __restrict__ q, int ld_q,
                        int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size,
                        float scale, int window, int num_pages, const float* __restrict__ sink,
                        const float* __restrict__ out_gate, int* __restrict__ status) {
-    __shared__ float q_smem[WARPS_PER_BLOCK][MAX_HEAD_DIM];
+    __shared__ float q_smem[WARPS_PER_BLOCK][MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long pair = (long long)blockIdx.x * WARPS_PER_BLOCK + warp;
     if (pair >= (long long)n_tokens * n_heads) return;
@@ -117,9 +119,9 @@ paged_attention_kernel(const T* __restrict__ q, int ld_q,
     __syncwarp();
 
     float m = -INFINITY, l = 0.0f;
-    float acc[MAX_HEAD_DIM / 32];
+    float acc[MAX_D / 32];
 #pragma unroll
-    for (int i = 0; i < MAX_HEAD_DIM / 32; i++) acc[i] = 0.0f;
+    for (int i = 0; i < MAX_D / 32; i++) acc[i] = 0.0f;
 
     for (int base = lo; base <= pos; base += 32) {
         const int j = base + lane;
@@ -141,14 +143,14 @@ paged_attention_kernel(const T* __restrict__ q, int ld_q,
         const float p = (valid && sc > -INFINITY) ? expf(sc - m_new) : 0.0f;
         l = l * corr + warp_sum(p);
 #pragma unroll
-        for (int i = 0; i < MAX_HEAD_DIM / 32; i++) acc[i] *= corr;
+        for (int i = 0; i < MAX_D / 32; i++) acc[i] *= corr;
         const int count = min(32, pos - base + 1);
         for (int jj = 0; jj < count; jj++) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const long long rj = __shfl_sync(0xffffffffu, row, jj);
             const T* vrow = v_cache + rj * head_dim;
 #pragma unroll
-            for (int i = 0; i < MAX_HEAD_DIM / 32; i++) {
+            for (int i = 0; i < MAX_D / 32; i++) {
                 const int d = lane + 32 * i;
                 if (d < head_dim) acc[i] = fmaf(pj, to_f32(vrow[d]), acc[i]);
             }
@@ -159,7 +161,7 @@ paged_attention_kernel(const T* __restrict__ q, int ld_q,
     if (sink) l += expf(sink[h] - m);
     const float inv = (out_gate ? out_gate[(size_t)t * n_heads + h] : 1.0f) / l;
 #pragma unroll
-    for (int i = 0; i < MAX_HEAD_DIM / 32; i++) {
+    for (int i = 0; i < MAX_D / 32; i++) {
         const int d = lane + 32 * i;
         if (d < head_dim) out[(size_t)t * ld_out + h * head_dim + d] = from_f32<T>(acc[i] * inv);
     }
@@ -206,13 +208,13 @@ SANDY_API int sandy_paged_attention_ext(const void* q, int ld_q, const void* k_c
     if (n_tokens == 0) return SANDY_OK;
     if (!q || !k_cache || !v_cache || !block_table || !token_seq || !positions || !out)
         return SANDY_ERR_ARGUMENT;
-    if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > MAX_HEAD_DIM) return SANDY_ERR_UNSUPPORTED;
+    if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > WIDE_HEAD_DIM) return SANDY_ERR_UNSUPPORTED;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || page_size <= 0 || window < 0) return SANDY_ERR_UNSUPPORTED;
     if (page_stride % head_dim != 0) return SANDY_ERR_UNSUPPORTED;
     const long long pairs = (long long)n_tokens * n_heads;
     const unsigned blocks = (unsigned)((pairs + WARPS_PER_BLOCK - 1) / WARPS_PER_BLOCK);
 #define LAUNCH(T)                                                                                     \
-    paged_attention_kernel<T><<<blocks, WARPS_PER_BLOCK * 32, 0, stream>>>(                           \
+    (head_dim <= MAX_HEAD_DIM ? paged_attention_kernel<T, MAX_HEAD_DIM> : paged_attention_kernel<T, WIDE_HEAD_DIM>)<<<blocks, WARPS_PER_BLOCK * 32, 0, stream>>>( \
         (const T*)q, ld_q, (const T*)k_cache, (const T*)v_cache, page_stride, block_table, max_blocks, \
         token_seq, positions, (T*)out, ld_out, n_tokens, n_heads, n_kv_heads, head_dim, page_size,    \
         scale, window, num_pages, sink, out_gate, status)

@@ -192,8 +192,8 @@ def paged_attention(q, k_cache, v_cache, block_table, token_seq, positions, out,
     _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out)
     hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
     T = q.shape[0]
-    if d % 16 != 0 or d > 256:
-        raise UnsupportedShape(f"attention: head size {d} must be a multiple of 16, at most 256")
+    if d % 16 != 0 or d > 640:
+        raise UnsupportedShape(f"attention: head size {d} must be a multiple of 16, at most 640")
     if n_heads % hkv != 0:
         raise UnsupportedShape(f"attention: {n_heads} heads do not divide into {hkv} key/value heads")
     if q.shape[1] != n_heads * d or out.shape != q.shape or q.stride(1) != 1 or out.stride(1) != 1 \
@@ -390,6 +390,87 @@ def glu(a, b, out, act: str = "silu") -> None:
                                                  ctypes.c_int(a.shape[0]), ctypes.c_int(a.shape[1]),
                                                  ctypes.c_int({"silu": 0, "gelu_tanh": 1}[act]), ctypes.c_int(_dt(a)), _stream())
     _check(code, "glu")
+
+
+def scale_add(y, gain, x, y2=None, gain2=None) -> None:
+    """x += gain * y (+ gain2 * y2), all float32; gains are [width]."""
+    _cuda(y, gain, x, y2, gain2)
+    for t, n in ((y, "y"), (gain, "gain"), (x, "x"), (y2, "y2"), (gain2, "gain2")):
+        _f32(t, n)
+    code = load_library("elementwise").sandy_scale_add(_p(y), ctypes.c_int(y.stride(0)), _p(gain), _p(y2),
+                                                       ctypes.c_int(0 if y2 is None else y2.stride(0)), _p(gain2), _p(x),
+                                                       ctypes.c_int(x.stride(0)), ctypes.c_int(x.shape[0]), ctypes.c_int(x.shape[1]),
+                                                       _stream())
+    _check(code, "scale_add")
+
+
+def head_product(a, w, out, *, n_groups: int, a_gcols: int, o_gcols: int) -> None:
+    """out[t, g * o_gcols + n] = sum_k w[g * N + n, k] * a[t, g * a_gcols + k]: one matrix [N, K] per head, stacked in w."""
+    _cuda(a, w, out)
+    N, K = w.shape[0] // n_groups, w.shape[1]
+    if a.dtype != w.dtype or w.shape[0] % n_groups or not w.is_contiguous() or a.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("head_product: a and w of one type, w [G * N, K] contiguous expected")
+    code = load_library("grouped_gemm").sandy_head_product(
+        _p(a), ctypes.c_int(a.stride(0)), ctypes.c_int(a_gcols), _p(w), ctypes.c_longlong(N * K), ctypes.c_int(K), _p(out),
+        ctypes.c_int(out.stride(0)), ctypes.c_int(o_gcols), ctypes.c_int(a.shape[0]), ctypes.c_int(n_groups), ctypes.c_int(N),
+        ctypes.c_int(K), ctypes.c_int(_dt(a)), ctypes.c_int(_dt(out)), _stream())
+    _check(code, f"head_product(G={n_groups},N={N},K={K})")
+
+
+@dataclasses.dataclass
+class Routing:
+    """The routing of a step's tokens to experts, as device arrays (int32 / float32); entry t * top + j is the j-th
+    choice of token t."""
+    n_tokens: int
+    n_experts: int
+    top: int
+    expert_of: torch.Tensor
+    weight_of: torch.Tensor
+    group_start: torch.Tensor
+    entry_of_slot: torch.Tensor
+    slot_of_entry: torch.Tensor
+
+
+def moe_route(logits, bias, top: int) -> Routing:
+    """Top-`top` experts of every token by float32 logits (+ bias), weights the softmax over the chosen; then the
+    entries grouped by expert."""
+    _cuda(logits, bias)
+    _f32(logits, "logits"); _f32(bias, "bias")
+    T, E = logits.shape
+    dev = logits.device
+    i32 = lambda n: torch.empty(n, dtype=torch.int32, device=dev)
+    r = Routing(T, E, top, i32(T * top), torch.empty(T * top, dtype=torch.float32, device=dev), i32(E + 1), i32(T * top), i32(T * top))
+    lib = load_library("moe")
+    _check(lib.sandy_moe_route(_p(logits), ctypes.c_int(logits.stride(0)), _p(bias), ctypes.c_int(T), ctypes.c_int(E), ctypes.c_int(top),
+                               _p(r.expert_of), _p(r.weight_of), _stream()), f"moe_route(E={E},top={top})")
+    _check(lib.sandy_moe_group(_p(r.expert_of), ctypes.c_int(T * top), ctypes.c_int(E), _p(r.group_start), _p(r.entry_of_slot),
+                               _p(r.slot_of_entry), _stream()), "moe_group")
+    return r
+
+
+def expert_product(r: Routing, a, w, out, *, gather: bool, act: str = "none") -> None:
+    """out[s] = act(W_e a[row(s)]) for the slots s of every expert e; w [E * N, K]; with `gather` a slot reads its
+    token's row of a [T, K], else row s of a [T * top, K].  act "none" | "relu_squared"."""
+    _cuda(a, w, out)
+    N, K = w.shape[0] // r.n_experts, w.shape[1]
+    if a.dtype != w.dtype or not w.is_contiguous() or a.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("expert_product: a and w of one type, w [E * N, K] contiguous expected")
+    code = load_library("grouped_gemm").sandy_expert_product(
+        _p(a), ctypes.c_int(a.stride(0)), _p(w), ctypes.c_longlong(N * K), ctypes.c_int(K), _p(out), ctypes.c_int(out.stride(0)),
+        ctypes.c_int(r.n_tokens * r.top), ctypes.c_int(r.n_experts), ctypes.c_int(N), ctypes.c_int(K), _p(r.group_start),
+        _p(r.entry_of_slot if gather else None), ctypes.c_int(r.top if gather else 1),
+        ctypes.c_int({"none": 0, "relu_squared": 1}[act]), ctypes.c_int(_dt(a)), ctypes.c_int(_dt(out)), _stream())
+    _check(code, f"expert_product(E={r.n_experts},N={N},K={K})")
+
+
+def moe_combine(r: Routing, rows, y, *, add: bool) -> None:
+    """y[t] (+)= sum_j weight[t, j] * rows[slot of (t, j)]; float32."""
+    _cuda(rows, y)
+    _f32(rows, "rows"); _f32(y, "y")
+    code = load_library("moe").sandy_moe_combine(_p(rows), ctypes.c_int(rows.stride(0)), _p(r.weight_of), _p(r.slot_of_entry),
+                                                 ctypes.c_int(r.n_tokens), ctypes.c_int(r.top), _p(y), ctypes.c_int(y.stride(0)),
+                                                 ctypes.c_int(y.shape[1]), ctypes.c_int(1 if add else 0), _stream())
+    _check(code, "moe_combine")
 
 
 def sample(logits, out_tokens, *, temperature=None, top_k=None, top_p=None, uniform=None, status=None,

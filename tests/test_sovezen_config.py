@@ -79,7 +79,7 @@ def _broken(path, value):
     (("layers", 0, "type"), "attention", "unknown layer type"),
     (("layers", 0, "mixer", "rot", "dims"), 7, "even"),
     (("layers", 0, "mixer", "rot", "dims"), 10, "at most"),
-    (("layers", 0, "mixer", "kv_rank"), 250, "at most 256"),
+    (("layers", 0, "mixer", "kv_rank"), 640, "at most 640"),
     (("layers", 1, "mixer", "q_rank"), KeyError, "q_rank"),
     (("layers", 1, "mlp", "router", "top"), 9, "top"),
     (("layers", 1, "mlp", "kind"), "routed", "dense"),

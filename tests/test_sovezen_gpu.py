@@ -223,6 +223,7 @@ ONE_LAYER = {
     "rotated, no feed-forward": lambda: [layer(rotated(3, 24, 8, 20, 40, base=30.0), None)],
     "query latent, no feed-forward": lambda: [layer(plain_queries(3, 24, 20, 40, 28), None)],
     "dense feed-forward": lambda: [layer(plain_queries(1, 8, 8, 16, 8), dense(72))],
+    "a latent wider than the tensor-core kernels take": lambda: [layer(rotated(2, 16, 48, 16, 296, base=1000.0), None)],
     "routed feed-forward": lambda: [layer(plain_queries(1, 8, 8, 16, 8), moe(6, 3, 24))],
 }
 
