@@ -13,9 +13,9 @@
 // and blocks beyond the step's tiles leave at once, so a recorded launch serves every routing.
 //
 // Two kernels.  bfloat16 operands whose rows start on 16-byte boundaries go through tensor cores (mma.sync
-// m16n8k16, 64 x 64 tiles, operands staged by cp.async in a ring of four stages and read with ldmatrix; rows a tile
-// does not have are zero-filled, so a decode step's one or two rows per expert cost a tile's weight traffic and
-// nothing else).  float32 operands and odd sizes take FFMA tiles.  Which kernel runs is a matter of the model's
+// m16n8k16; tiles of 64 x 64, or 128 x 64 where the groups are long; operands staged by cp.async in a ring of
+// stages and read with ldmatrix; rows a tile does not have are zero-filled, so a decode step's one or two rows per
+// expert cost a tile's weight traffic and nothing else).  float32 operands and odd sizes take FFMA tiles.  Which kernel runs is a matter of the model's
 // sizes alone, never of a step's rows.
 #include "common.cuh"
 
@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(THREADS) grouped_tile_kernel(GroupedArgs p) {
 }
 
 // ---- tensor-core tiles (bfloat16) ---------------------------------------------------------------------------------
-constexpr int MM = 64, MN = 64, MK = 32, MSTAGES = 4, MPITCH = MK + 8, MTHREADS = 128;
+constexpr int MN = 64, MK = 32, MPITCH = MK + 8, MTHREADS = 128;
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
     const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
@@ -139,8 +139,14 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <typename TO>
+__device__ __forceinline__ void store_pair(float* dst, float a, float b) { *reinterpret_cast<float2*>(dst) = make_float2(a, b); }
+__device__ __forceinline__ void store_pair(bf16* dst, float a, float b) { *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(a, b); }
+
+// MT: row tiles of 16 a warp owns (2: blocks of 64 rows behind a ring of four stages; 4: blocks of 128 rows, which
+// feed twice the products from the same weight fragments, behind a ring of three).
+template <typename TO, int MT>
 __global__ void __launch_bounds__(MTHREADS) grouped_mma_kernel(GroupedArgs p) {
+    constexpr int MM = 32 * MT, MSTAGES = MT == 2 ? 4 : 3;
     __shared__ __align__(16) bf16 sA[MSTAGES][MM][MPITCH];
     __shared__ __align__(16) bf16 sB[MSTAGES][MN][MPITCH];
     __shared__ int s_rows[MM];
@@ -168,23 +174,27 @@ __global__ void __launch_bounds__(MTHREADS) grouped_mma_kernel(GroupedArgs p) {
         row_end = p.rows;
     }
     const int n0 = blockIdx.x * MN;
-    if (tid < MM) {
-        const int s = row0 + tid;
+    for (int i = tid; i < MM; i += MTHREADS) {
+        const int s = row0 + i;
         int r = -1;
         if (s < row_end) r = p.a_row ? p.a_row[s] / p.a_row_div : s;
-        s_rows[tid] = r;
+        s_rows[i] = r;
     }
     __syncthreads();
     const bf16* A = (const bf16*)p.a + (size_t)g * p.a_gcols;
     const bf16* W = (const bf16*)p.w + (size_t)g * p.w_gstride;
-    // a stage: 64 rows x 4 pieces of 8 for each operand; a thread copies two pieces of each
+    // a stage: rows x 4 pieces of 8 for each operand
     auto load_stage = [&](int stage, int k0) {
 #pragma unroll
-        for (int i = 0; i < 2; i++) {
+        for (int i = 0; i < MM * 4 / MTHREADS; i++) {
             const int c = tid + i * MTHREADS, r = c >> 2, kc = (c & 3) * 8;
             const int ar = s_rows[r];
             const bool va = ar >= 0 && k0 + kc < p.K;
             cp_async_16(&sA[stage][r][kc], va ? (const void*)(A + (size_t)ar * p.lda + k0 + kc) : (const void*)A, va);
+        }
+#pragma unroll
+        for (int i = 0; i < MN * 4 / MTHREADS; i++) {
+            const int c = tid + i * MTHREADS, r = c >> 2, kc = (c & 3) * 8;
             const int n = n0 + r;
             const bool vb = n < p.N && k0 + kc < p.K;
             cp_async_16(&sB[stage][r][kc], vb ? (const void*)(W + (size_t)n * p.ldw + k0 + kc) : (const void*)W, vb);
@@ -198,8 +208,8 @@ __global__ void __launch_bounds__(MTHREADS) grouped_mma_kernel(GroupedArgs p) {
         else asm volatile("cp.async.commit_group;" ::: "memory");
     }
     const int warp = tid >> 5, lane = tid & 31;
-    const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
-    float acc[2][4][4] = {};
+    const int wm = (warp >> 1) * (16 * MT), wn = (warp & 1) * 32;
+    float acc[MT][4][4] = {};
     for (int kt = 0; kt < n_k; kt++) {
         asm volatile("cp.async.wait_group %0;" ::"n"(MSTAGES - 2) : "memory");
         __syncthreads();                             // stage kt has landed for everyone, stage kt - 1 has been read by everyone
@@ -208,15 +218,15 @@ __global__ void __launch_bounds__(MTHREADS) grouped_mma_kernel(GroupedArgs p) {
         const int st = kt % MSTAGES;
 #pragma unroll
         for (int kk = 0; kk < MK; kk += 16) {
-            unsigned a[2][4], b[2][4];
+            unsigned a[MT][4], b[2][4];
 #pragma unroll
-            for (int mt = 0; mt < 2; mt++)
+            for (int mt = 0; mt < MT; mt++)
                 ldmatrix_x4(a[mt], &sA[st][wm + mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][kk + (lane >> 4) * 8]);
 #pragma unroll
             for (int np = 0; np < 2; np++)
                 ldmatrix_x4(b[np], &sB[st][wn + np * 16 + (lane & 7) + (lane >> 4) * 8][kk + ((lane >> 3) & 1) * 8]);
 #pragma unroll
-            for (int mt = 0; mt < 2; mt++)
+            for (int mt = 0; mt < MT; mt++)
 #pragma unroll
                 for (int nt = 0; nt < 4; nt++) mma_bf16(acc[mt][nt], a[mt], b[nt >> 1][(nt & 1) * 2], b[nt >> 1][(nt & 1) * 2 + 1]);
         }
@@ -224,25 +234,33 @@ __global__ void __launch_bounds__(MTHREADS) grouped_mma_kernel(GroupedArgs p) {
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     TO* O = (TO*)p.out + (size_t)g * p.o_gcols;
     const int gq = lane >> 2, tq = lane & 3;
+    // a thread holds pairs of neighbouring columns: one store a pair where every pair starts on a pair's boundary
+    const bool pairs = !(p.ldo & 1) && !(p.o_gcols & 1) && !((uintptr_t)p.out % (2 * sizeof(TO)));
+    auto finish = [&](float v) {
+        if (p.act == 1) {
+            v = fmaxf(v, 0.0f);
+            v = v * v;
+        }
+        return v;
+    };
 #pragma unroll
-    for (int mt = 0; mt < 2; mt++)
+    for (int mt = 0; mt < MT; mt++)
 #pragma unroll
         for (int half = 0; half < 2; half++) {
             const int s = row0 + wm + mt * 16 + gq + half * 8;
             if (s >= row_end) continue;
 #pragma unroll
-            for (int nt = 0; nt < 4; nt++)
-#pragma unroll
-                for (int j = 0; j < 2; j++) {
-                    const int n = n0 + wn + nt * 8 + tq * 2 + j;
-                    if (n >= p.N) continue;
-                    float v = acc[mt][nt][half * 2 + j];
-                    if (p.act == 1) {
-                        v = fmaxf(v, 0.0f);
-                        v = v * v;
-                    }
-                    O[(size_t)s * p.ldo + n] = from_f32<TO>(v);
+            for (int nt = 0; nt < 4; nt++) {
+                const int n = n0 + wn + nt * 8 + tq * 2;
+                const float v0 = finish(acc[mt][nt][half * 2]), v1 = finish(acc[mt][nt][half * 2 + 1]);
+                TO* dst = O + (size_t)s * p.ldo + n;
+                if (pairs && n + 1 < p.N) {
+                    store_pair(dst, v0, v1);
+                } else {
+                    if (n < p.N) dst[0] = from_f32<TO>(v0);
+                    if (n + 1 < p.N) dst[1] = from_f32<TO>(v1);
                 }
+            }
         }
 }
 
@@ -261,10 +279,17 @@ int launch(const GroupedArgs& p, dim3 grid, cudaStream_t stream) {
 template <typename F>
 int dispatch(const GroupedArgs& p, F row_tiles, int groups_z, int in_dtype, int out_dtype, cudaStream_t stream) {
     if (in_dtype == SANDY_BF16 && mma_takes(p)) {
-        const dim3 grid((p.N + MN - 1) / MN, row_tiles(MM), groups_z);
+        // Blocks of 128 rows where the groups are long (a prompt step), of 64 otherwise.  Both add an element's
+        // products in the same order, so the choice never changes a result.
+        const bool tall = row_tiles(1) / (p.group_start ? p.G : 1) >= 96;
+        const dim3 grid((p.N + MN - 1) / MN, row_tiles(tall ? 128 : 64), groups_z);
         if (grid.y > 65535) return SANDY_ERR_UNSUPPORTED;
-        if (out_dtype == SANDY_BF16) return sandy_launch(grouped_mma_kernel<bf16>, grid, dim3(MTHREADS), 0, stream, p);
-        if (out_dtype == SANDY_F32) return sandy_launch(grouped_mma_kernel<float>, grid, dim3(MTHREADS), 0, stream, p);
+        if (out_dtype == SANDY_BF16)
+            return tall ? sandy_launch(grouped_mma_kernel<bf16, 4>, grid, dim3(MTHREADS), 0, stream, p)
+                        : sandy_launch(grouped_mma_kernel<bf16, 2>, grid, dim3(MTHREADS), 0, stream, p);
+        if (out_dtype == SANDY_F32)
+            return tall ? sandy_launch(grouped_mma_kernel<float, 4>, grid, dim3(MTHREADS), 0, stream, p)
+                        : sandy_launch(grouped_mma_kernel<float, 2>, grid, dim3(MTHREADS), 0, stream, p);
         return SANDY_ERR_UNSUPPORTED;
     }
     const dim3 grid((p.N + TN - 1) / TN, row_tiles(TM), groups_z);

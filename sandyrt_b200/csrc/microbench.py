@@ -3,6 +3,7 @@
     python -m sandyrt_b200.csrc.microbench decode-attention [--heads 12] [--head-dim 64] [--page-size 16]
     python -m sandyrt_b200.csrc.microbench gemm [--rows 2048] [--width 768] [--inner 3072] [--layers 48] [--k-sweep]
     python -m sandyrt_b200.csrc.microbench prefill-attention [--heads 12] [--page-size 16] [--shape 2x1024+0 ...]
+    python -m sandyrt_b200.csrc.microbench grouped [--tokens 2048 8] [--experts 16] [--top 2] [--width 1536] [--inner 2048]
 
 decode-attention: the register kernel and the bulk-copy kernel of single-token attention on
 several (tokens, context) shapes.  Each timing replays a graph of one launch per distinct cache
@@ -182,6 +183,35 @@ def prefill_attention(a) -> int:
     return 0
 
 
+def grouped(a) -> int:
+    """The products with one matrix per expert and per head, alone: an expert's up-projection (rows gathered by the
+    routing, relu squared) and down-projection on `layers` distinct sets of weights, and the two per-head products of
+    attention over a latent.  Bytes: the matrices that are read at least once plus the rows in and out."""
+    dev = torch.device("cuda:0")
+    E, top, W, F, L = a.experts, a.top, a.width, a.inner, a.layers
+    g = torch.Generator(device="cpu").manual_seed(0)
+    ups = [(torch.randn(E * F, W, generator=g) * W ** -0.5).to(torch.bfloat16).to(dev) for _ in range(L)]
+    downs = [(torch.randn(E * W, F, generator=g) * F ** -0.5).to(torch.bfloat16).to(dev) for _ in range(L)]
+    for T in a.tokens:
+        h = torch.randn(T, W, generator=g).to(torch.bfloat16).to(dev)
+        r = ops.moe_route(torch.randn(T, E, generator=g).to(dev), None, top)
+        inner = torch.empty(T * top, F, dtype=torch.bfloat16, device=dev)
+        rows = torch.empty(T * top, W, dtype=torch.float32, device=dev)
+        used = min(E, T * top)
+        for name, fn, byts in (
+                ("up", lambda l: ops.expert_product(r, h, ups[l], inner, gather=True, act="relu_squared"), used * F * W * 2 + T * top * (W + F) * 2),
+                ("down", lambda l: ops.expert_product(r, inner, downs[l], rows, gather=False), used * F * W * 2 + T * top * (2 * F + 4 * W))):
+            us = _time_graph(fn, L)
+            print(f"expert {name:4s} T={T:5d} E={E} top={top} {W}x{F}: {us:8.1f} us  {2.0 * T * top * W * F / us / 1e6:7.1f} TFLOP/s  {byts / us / 1e3:7.0f} GB/s")
+        H, d, c, pad = a.heads, 64, 96, 128
+        q = torch.randn(T, H * (d + 32), generator=g).to(torch.bfloat16).to(dev)
+        uk = [(torch.randn(H * c, d, generator=g) * d ** -0.5).to(torch.bfloat16).to(dev) for _ in range(L)]
+        q_abs = torch.empty(T, H * pad, dtype=torch.bfloat16, device=dev)
+        us = _time_graph(lambda l: ops.head_product(q, uk[l], q_abs, n_groups=H, a_gcols=d + 32, o_gcols=pad), L)
+        print(f"head   q->latent T={T:5d} H={H} {c}x{d}: {us:8.1f} us  {2.0 * T * H * c * d / us / 1e6:7.1f} TFLOP/s  {(T * H * (d + c) * 2 + H * c * d * 2) / us / 1e3:7.0f} GB/s")
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="sandyrt_b200.csrc.microbench")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -206,6 +236,15 @@ def main(argv=None) -> int:
     pa.add_argument("--shape", nargs="+", default=["2x1024+0", "8x256+0", "4x512+512", "16x128+0", "2x2048+0", "1x8192+0"],
                     help="REQUESTSxNEW+CACHED")
     pa.set_defaults(fn=prefill_attention)
+    gr = sub.add_parser("grouped")
+    gr.add_argument("--tokens", type=int, nargs="+", default=[2048, 8])
+    gr.add_argument("--experts", type=int, default=16)
+    gr.add_argument("--top", type=int, default=2)
+    gr.add_argument("--width", type=int, default=1536)
+    gr.add_argument("--inner", type=int, default=2048)
+    gr.add_argument("--heads", type=int, default=24)
+    gr.add_argument("--layers", type=int, default=4, help="distinct sets of weights (together larger than L2)")
+    gr.set_defaults(fn=grouped)
     a = ap.parse_args(argv)
     return a.fn(a)
 
