@@ -693,16 +693,40 @@ void moe_route(const Launch& l, const Tensor& logits, const Tensor* bias, const 
     check(group(r.expert_of, r.n_tokens * r.top, r.n_experts, r.group_start, r.entry_of_slot, r.slot_of_entry, l.stream), "moe_group");
 }
 
-void expert_product(const Launch& l, const Routing& r, const Tensor& a, bool gather, const Tensor& w, ExpertAct act, Tensor& out) {
+void expert_product(const Launch& l, const Routing& r, const Tensor& a, bool gather, const Tensor& w, ExpertAct act, Tensor& out,
+                    Tensor* sorted) {
     if (r.n_experts <= 0 || w.rows % r.n_experts) throw KernelError("expert_product: the weight's rows do not divide into the experts");
     const int64_t N = w.rows / r.n_experts, K = w.cols, slots = (int64_t)r.n_tokens * r.top;
     if (a.dtype != w.dtype || a.cols != K || a.rows != (gather ? r.n_tokens : slots) || out.rows != slots || out.cols != N ||
         (out.dtype != a.dtype && out.dtype != DType::F32))
         throw KernelError("expert_product: a " + dims(a) + ", w " + dims(w) + " and out " + dims(out) + " disagree");
     if (left_out("product", N, K)) return;
-    static auto fn = SANDY_KERNEL(grouped_gemm, sandy_expert_product);
     // bytes: every expert's matrix at most once, and no more matrices than slots
     const double matrices = std::min<double>(r.n_experts, (double)slots);
+    static const int tc_mode = env_int("SANDYRT_EXPERT_TC", -1);      // 0 / 1 force one kernel, for comparisons
+    const bool many = tc_mode < 0 ? slots >= (int64_t)kExpertTcRows * r.n_experts : tc_mode == 1;
+    if (many && a.dtype == DType::BF16 && K % 8 == 0 && w.ld % 8 == 0 && !((uintptr_t)w.data & 15) && (!gather || sorted)) {
+        const Tensor* rows = &a;
+        if (gather) {
+            if (sorted->dtype != a.dtype || sorted->rows != slots || sorted->cols != K) throw KernelError("expert_product: the scratch for sorted rows must be [slots, K] of a's type");
+            static auto gather_fn = SANDY_KERNEL(moe, sandy_moe_gather);
+            OpTimer timer(l, "expert rows, sorted", 2.0 * tensor_bytes(sorted), 0);
+            check(gather_fn(a.data, (long long)a.ld * (long long)a.elem_size(), r.entry_of_slot, r.top, sorted->data,
+                            (long long)sorted->ld * (long long)sorted->elem_size(), (int)slots, (int)(K * a.elem_size()), l.stream),
+                  "moe_gather");
+            rows = sorted;
+        }
+        if (rows->ld % 8 == 0 && !((uintptr_t)rows->data & 15)) {
+            static auto tc = SANDY_KERNEL(grouped_gemm_tc, sandy_expert_product_tc);
+            OpTimer timer(l, "product per expert (tcgen05)", matrices * N * K * w.elem_size() + (double)slots * (K * a.elem_size() + N * out.elem_size()),
+                          2.0 * slots * N * K);
+            check(tc(rows->data, (int)rows->ld, w.data, (int)w.ld, out.data, (int)out.ld, (int)slots, r.n_experts, (int)N, (int)K, r.group_start,
+                     (int)act, code_of(out.dtype), l.kernel_status, l.stream),
+                  "expert_product_tc(E=" + std::to_string(r.n_experts) + ",N=" + std::to_string(N) + ",K=" + std::to_string(K) + ")");
+            return;
+        }
+    }
+    static auto fn = SANDY_KERNEL(grouped_gemm, sandy_expert_product);
     OpTimer timer(l, "product per expert", matrices * N * K * w.elem_size() + (double)slots * (K * a.elem_size() + N * out.elem_size()),
                   2.0 * slots * N * K);
     check(fn(a.data, (int)a.ld, w.data, (long long)N * w.ld, (int)w.ld, out.data, (int)out.ld, (int)slots, r.n_experts, (int)N, (int)K,

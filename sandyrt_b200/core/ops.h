@@ -200,7 +200,12 @@ void moe_route(const Launch& l, const Tensor& logits, const Tensor* bias, const 
 enum class ExpertAct : int { None = 0, ReluSquared = 1 };
 // out[s] = act(W_e a[row(s)]) for the slots s of every expert e; w [E * N, K]; with `gather` a slot reads its token's
 // row of `a` ([T, K]), else row s ([T * top, K]).  out [T * top, N].
-void expert_product(const Launch& l, const Routing& r, const Tensor& a, bool gather, const Tensor& w, ExpertAct act, Tensor& out);
+// Steps with many rows an expert (kExpertTcRows on average) run on tcgen05 (grouped_gemm_tc.cu), which wants an
+// expert's rows one after another: with `gather` the rows are first copied into `sorted` ([T * top, K] of a's type;
+// without it such steps stay on the mma.sync tiles).  Fewer rows, float32 and odd sizes take grouped_gemm.cu.
+constexpr int kExpertTcRows = 48;
+void expert_product(const Launch& l, const Routing& r, const Tensor& a, bool gather, const Tensor& w, ExpertAct act, Tensor& out,
+                    Tensor* sorted = nullptr);
 // y[t] (+)= sum_j weight[t, j] * rows[slot of (t, j)]; rows float32 [T * top, width], y float32 [T, width].
 void moe_combine(const Launch& l, const Routing& r, const Tensor& rows, Tensor& y, bool add);
 

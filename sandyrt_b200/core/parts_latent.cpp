@@ -202,7 +202,8 @@ public:
         r.slot_of_entry = (int*)ws.raw("moe_slot_of_entry", (size_t)slots * sizeof(int));
         ops::moe_route(l, logits, has_bias_ ? &bias_.view : nullptr, r);
         Tensor a = ws.get("moe_inner", slots, inner_, ctx.compute_dtype);
-        ops::expert_product(l, r, h.tensor(), true, up_.view, ops::ExpertAct::ReluSquared, a);
+        Tensor sorted = ws.get("moe_sorted_rows", slots, width_, ctx.compute_dtype);      // for steps whose products want them
+        ops::expert_product(l, r, h.tensor(), true, up_.view, ops::ExpertAct::ReluSquared, a, &sorted);
         Tensor rows = ws.get("moe_rows", slots, width_, DType::F32);
         ops::expert_product(l, r, a, false, down_.view, ops::ExpertAct::None, rows);
         ops::moe_combine(l, r, rows, x, !ctx.overwrite);

@@ -53,6 +53,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "matrix_state": [],
     "latent_prepare": [],
     "grouped_gemm": [],
+    "grouped_gemm_tc": [],
     "moe": [],
 }
 

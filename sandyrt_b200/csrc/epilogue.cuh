@@ -3,7 +3,7 @@
 
 #include "common.cuh"
 
-enum SandyAct : int { SANDY_ACT_NONE = 0, SANDY_ACT_GELU_TANH = 1, SANDY_ACT_GELU_ERF = 2 };
+enum SandyAct : int { SANDY_ACT_NONE = 0, SANDY_ACT_GELU_TANH = 1, SANDY_ACT_GELU_ERF = 2, SANDY_ACT_RELU_SQUARED = 3 };
 
 // gelu_new, in the reference's order of operations (src/ir/BuiltinLowering.cpp:116-140):
 //   x2 = u*u; x3 = x2*u; inner = u + 0.044715*x3; t = tanh(0.7978845608028654*inner);

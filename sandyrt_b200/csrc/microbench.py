@@ -203,6 +203,14 @@ def grouped(a) -> int:
                 ("down", lambda l: ops.expert_product(r, inner, downs[l], rows, gather=False), used * F * W * 2 + T * top * (2 * F + 4 * W))):
             us = _time_graph(fn, L)
             print(f"expert {name:4s} T={T:5d} E={E} top={top} {W}x{F}: {us:8.1f} us  {2.0 * T * top * W * F / us / 1e6:7.1f} TFLOP/s  {byts / us / 1e3:7.0f} GB/s")
+        sorted_rows = torch.empty(T * top, W, dtype=torch.bfloat16, device=dev)
+        ops.moe_gather(r, h, sorted_rows)
+        for name, fn in (("up", lambda l: ops.expert_product_tc(r, sorted_rows, ups[l], inner, act="relu_squared")),
+                         ("down", lambda l: ops.expert_product_tc(r, inner, downs[l], rows))):
+            us = _time_graph(fn, L)
+            print(f"expert {name:4s} T={T:5d} tcgen05: {us:8.1f} us  {2.0 * T * top * W * F / us / 1e6:7.1f} TFLOP/s")
+        us = _time_graph(lambda l: ops.moe_gather(r, h, sorted_rows), 1)
+        print(f"expert rows gathered T={T:5d}: {us:8.1f} us")
         H, d, c, pad = a.heads, 64, 96, 128
         q = torch.randn(T, H * (d + 32), generator=g).to(torch.bfloat16).to(dev)
         uk = [(torch.randn(H * c, d, generator=g) * d ** -0.5).to(torch.bfloat16).to(dev) for _ in range(L)]

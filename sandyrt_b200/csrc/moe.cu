@@ -7,6 +7,8 @@
 //                      entry_of_slot and slot_of_entry are the two directions of the permutation.  Which slot of
 //                      its expert an entry gets is not fixed from run to run; nothing depends on it, since every
 //                      slot's row is computed on its own.
+//   sandy_moe_gather   sorted[s] = x[token of slot s]: the tokens' rows in the order of the slots, for a product that
+//                      wants every expert's rows one after another.
 //   sandy_moe_combine  y[t] (+)= sum_j weight[t, j] * rows[slot_of_entry[t * top + j]], in 32-bit, j in order.
 #include "common.cuh"
 
@@ -85,6 +87,19 @@ moe_group_kernel(const int* __restrict__ expert_of, int n_entries, int n_experts
     }
 }
 
+template <typename V>
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(const V* __restrict__ x, long long ldx, const int* __restrict__ entry_of_slot, int top, V* __restrict__ out,
+                  long long ldo, int n_slots, int cols) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long long n = (long long)n_slots * cols;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long s = i / cols, c = i % cols;
+        out[s * ldo + c] = x[(long long)(entry_of_slot[s] / top) * ldx + c];
+    }
+}
+
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ rows, int ld_rows, const float* __restrict__ weight_of,
                    const int* __restrict__ slot_of_entry, int top, float* __restrict__ y, int ldy, int width, int add) {
@@ -131,4 +146,24 @@ SANDY_API int sandy_moe_combine(const float* rows, int ld_rows, const float* wei
     if (!rows || !weight_of || !slot_of_entry || !y) return SANDY_ERR_ARGUMENT;
     return sandy_launch(moe_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, rows, ld_rows, weight_of, slot_of_entry, top,
                         y, ldy, width, add);
+}
+
+// x: [tokens, bytes_per_row] and out: [n_slots, bytes_per_row] as raw bytes with pitches in bytes; pieces of 16 bytes
+// where everything is aligned so, else of 2.
+SANDY_API int sandy_moe_gather(const void* x, long long pitch_x, const int* entry_of_slot, int top, void* out, long long pitch_out,
+                               int n_slots, int bytes_per_row, cudaStream_t stream) {
+    if (n_slots == 0 || bytes_per_row == 0) return SANDY_OK;
+    if (!x || !entry_of_slot || !out || top < 1) return SANDY_ERR_ARGUMENT;
+    const bool wide = !(bytes_per_row % 16) && !(pitch_x % 16) && !(pitch_out % 16) && !((uintptr_t)x & 15) && !((uintptr_t)out & 15);
+    const int unit = wide ? 16 : 2;
+    if (bytes_per_row % unit || pitch_x % unit || pitch_out % unit) return SANDY_ERR_UNSUPPORTED;
+    const long long n = (long long)n_slots * (bytes_per_row / unit);
+    long long blocks = (n + 255) / 256;
+    const long long cap = (long long)sandy_sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    if (wide)
+        return sandy_launch(moe_gather_kernel<uint4>, dim3((unsigned)blocks), dim3(256), 0, stream, (const uint4*)x, pitch_x / 16,
+                            entry_of_slot, top, (uint4*)out, pitch_out / 16, n_slots, bytes_per_row / 16);
+    return sandy_launch(moe_gather_kernel<unsigned short>, dim3((unsigned)blocks), dim3(256), 0, stream, (const unsigned short*)x,
+                        pitch_x / 2, entry_of_slot, top, (unsigned short*)out, pitch_out / 2, n_slots, bytes_per_row / 2);
 }

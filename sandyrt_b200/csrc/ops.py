@@ -463,6 +463,32 @@ def expert_product(r: Routing, a, w, out, *, gather: bool, act: str = "none") ->
     _check(code, f"expert_product(E={r.n_experts},N={N},K={K})")
 
 
+def moe_gather(r: Routing, x, out) -> None:
+    """out[s] = x[token of slot s]: the tokens' rows in the order of the slots."""
+    _cuda(x, out)
+    if x.dtype != out.dtype or x.stride(1) != 1 or out.stride(1) != 1 or out.shape != (r.n_tokens * r.top, x.shape[1]):
+        raise KernelError("moe_gather: out must be [tokens * top, cols] of x's type")
+    es = x.element_size()
+    code = load_library("moe").sandy_moe_gather(_p(x), ctypes.c_longlong(x.stride(0) * es), _p(r.entry_of_slot), ctypes.c_int(r.top), _p(out),
+                                                ctypes.c_longlong(out.stride(0) * es), ctypes.c_int(out.shape[0]),
+                                                ctypes.c_int(x.shape[1] * es), _stream())
+    _check(code, "moe_gather")
+
+
+def expert_product_tc(r: Routing, a_sorted, w, out, *, act: str = "none") -> None:
+    """The per-expert product on tcgen05: a_sorted bfloat16 [T * top, K] with every expert's rows one after another
+    (moe_gather), w bfloat16 [E * N, K], out [T * top, N] bfloat16 or float32."""
+    _cuda(a_sorted, w, out)
+    N, K = w.shape[0] // r.n_experts, w.shape[1]
+    if a_sorted.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not w.is_contiguous() or a_sorted.stride(1) != 1 or out.stride(1) != 1:
+        raise UnsupportedShape("expert_product_tc takes bfloat16 operands, w [E * N, K] contiguous")
+    code = load_library("grouped_gemm_tc").sandy_expert_product_tc(
+        _p(a_sorted), ctypes.c_int(a_sorted.stride(0)), _p(w), ctypes.c_int(K), _p(out), ctypes.c_int(out.stride(0)),
+        ctypes.c_int(r.n_tokens * r.top), ctypes.c_int(r.n_experts), ctypes.c_int(N), ctypes.c_int(K), _p(r.group_start),
+        ctypes.c_int({"none": 0, "relu_squared": 1}[act]), ctypes.c_int(_dt(out)), _p(kernel_status(out.device)), _stream())
+    _check(code, f"expert_product_tc(E={r.n_experts},N={N},K={K})")
+
+
 def moe_combine(r: Routing, rows, y, *, add: bool) -> None:
     """y[t] (+)= sum_j weight[t, j] * rows[slot of (t, j)]; float32."""
     _cuda(rows, y)

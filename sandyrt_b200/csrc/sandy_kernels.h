@@ -179,11 +179,17 @@ int sandy_expert_product(const void* a, int lda, const void* w, long long w_gstr
                          int n_groups, int N, int K, const int* group_start, const int* a_row, int a_row_div, int act,
                          int in_dtype, int out_dtype, cudaStream_t stream);
 
+/* grouped_gemm_tc.cu */
+int sandy_expert_product_tc(const void* a, int lda, const void* w, int ldw, void* out, int ldo, int n_slots, int n_groups, int N,
+                            int K, const int* group_start, int act, int out_dtype, int* status, cudaStream_t stream);
+
 /* moe.cu */
 int sandy_moe_route(const float* logits, int ld, const float* bias, int n_tokens, int n_experts, int top, int* expert_of,
                     float* weight_of, cudaStream_t stream);
 int sandy_moe_group(const int* expert_of, int n_entries, int n_experts, int* group_start, int* entry_of_slot, int* slot_of_entry,
                     cudaStream_t stream);
+int sandy_moe_gather(const void* x, long long pitch_x, const int* entry_of_slot, int top, void* out, long long pitch_out, int n_slots,
+                     int bytes_per_row, cudaStream_t stream);
 int sandy_moe_combine(const float* rows, int ld_rows, const float* weight_of, const int* slot_of_entry, int n_tokens, int top,
                       float* y, int ldy, int width, int add, cudaStream_t stream);
 

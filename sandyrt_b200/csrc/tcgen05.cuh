@@ -171,6 +171,10 @@ template <int ACT>
 __device__ __forceinline__ float act_of(float v) {
     if (ACT == SANDY_ACT_GELU_TANH) return gelu_tanh_fast(v);
     if (ACT == SANDY_ACT_GELU_ERF) return gelu_erf(v);
+    if (ACT == SANDY_ACT_RELU_SQUARED) {
+        v = fmaxf(v, 0.0f);
+        return v * v;
+    }
     return v;
 }
 

@@ -75,6 +75,34 @@ def test_routed_experts_from_logits_to_sum(T, E, top, width, ff, dtype, tol):
     assert torch.allclose(y2, y - 0.5, atol=1e-5)
 
 
+@pytest.mark.parametrize("T,E,top,width,ff", [(300, 16, 4, 64, 96), (1, 4, 2, 32, 16), (700, 5, 2, 200, 136), (1500, 3, 1, 72, 40)])
+def test_expert_products_on_tcgen05(T, E, top, width, ff):
+    """The same two products through the tcgen05 kernel (rows gathered into the slots' order first), against float32
+    PyTorch and against the mma.sync tiles: groups that start anywhere, tiles cut by a group's end and by N."""
+    dtype = torch.bfloat16
+    h = _rand(T, width, dtype=dtype, seed=3)
+    r = ops.moe_route(_rand(T, E, seed=4, scale=2.0), None, top)
+    up = _rand(E * ff, width, dtype=dtype, seed=6, scale=width ** -0.5)
+    down = _rand(E * width, ff, dtype=dtype, seed=7, scale=ff ** -0.5)
+    sorted_rows = torch.empty(T * top, width, dtype=dtype, device=DEV)
+    ops.moe_gather(r, h, sorted_rows)
+    token_of_slot = (r.entry_of_slot.long() // top)
+    assert torch.equal(sorted_rows, h[token_of_slot])
+    inner = torch.full((T * top, ff), 3.0, dtype=dtype, device=DEV)
+    ops.expert_product_tc(r, sorted_rows, up, inner, act="relu_squared")
+    inner_mma = torch.empty_like(inner)
+    ops.expert_product(r, h, up, inner_mma, gather=True, act="relu_squared")
+    expert_of_slot = r.expert_of.long()[r.entry_of_slot.long()]
+    want = torch.relu(torch.einsum("sk,snk->sn", sorted_rows.float(), up.float().view(E, ff, width)[expert_of_slot])) ** 2
+    assert torch.allclose(inner.float(), want, atol=2e-2, rtol=2e-2)
+    assert torch.allclose(inner.float(), inner_mma.float(), atol=2e-2, rtol=2e-2)
+    rows = torch.full((T * top, width), 3.0, dtype=torch.float32, device=DEV)
+    ops.expert_product_tc(r, inner, down, rows)
+    want = torch.einsum("sk,snk->sn", inner.float(), down.float().view(E, width, ff)[expert_of_slot])
+    assert torch.allclose(rows, want, atol=2e-2, rtol=2e-2)
+    ops.check_kernel_status(rows.device)
+
+
 def test_equal_logits_go_to_the_lower_expert():
     logits = torch.zeros(3, 6, device=DEV)
     logits[1, 4] = logits[1, 2] = 1.0
