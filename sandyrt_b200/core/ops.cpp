@@ -704,8 +704,7 @@ void expert_product(const Launch& l, const Routing& r, const Tensor& a, bool gat
     // bytes: every expert's matrix at most once, and no more matrices than slots
     const double matrices = std::min<double>(r.n_experts, (double)slots);
     static const int tc_mode = env_int("SANDYRT_EXPERT_TC", -1);      // 0 / 1 force one kernel, for comparisons
-    const bool many = tc_mode < 0 ? slots >= (int64_t)kExpertTcRows * r.n_experts : tc_mode == 1;
-    if (many && a.dtype == DType::BF16 && K % 8 == 0 && w.ld % 8 == 0 && !((uintptr_t)w.data & 15) && (!gather || sorted)) {
+    if (tc_mode != 0 && a.dtype == DType::BF16 && K % 8 == 0 && w.ld % 8 == 0 && !((uintptr_t)w.data & 15) && (!gather || sorted)) {
         const Tensor* rows = &a;
         if (gather) {
             if (sorted->dtype != a.dtype || sorted->rows != slots || sorted->cols != K) throw KernelError("expert_product: the scratch for sorted rows must be [slots, K] of a's type");

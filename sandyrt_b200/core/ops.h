@@ -200,10 +200,13 @@ void moe_route(const Launch& l, const Tensor& logits, const Tensor* bias, const 
 enum class ExpertAct : int { None = 0, ReluSquared = 1 };
 // out[s] = act(W_e a[row(s)]) for the slots s of every expert e; w [E * N, K]; with `gather` a slot reads its token's
 // row of `a` ([T, K]), else row s ([T * top, K]).  out [T * top, N].
-// Steps with many rows an expert (kExpertTcRows on average) run on tcgen05 (grouped_gemm_tc.cu), which wants an
+// bfloat16 products whose rows start on 16-byte boundaries run on tcgen05 (grouped_gemm_tc.cu), which wants an
 // expert's rows one after another: with `gather` the rows are first copied into `sorted` ([T * top, K] of a's type;
-// without it such steps stay on the mma.sync tiles).  Fewer rows, float32 and odd sizes take grouped_gemm.cu.
-constexpr int kExpertTcRows = 48;
+// without that scratch the product stays on the mma.sync tiles).  float32 and odd sizes take grouped_gemm.cu.
+// The tcgen05 kernel is ahead at every step size, the copy included (width 1,536, 16 experts of 2,048, 2 a token; us
+// for the up- and the down-projection, mma.sync tiles / tcgen05): 8,192 tokens 379 + 374 / 117 + 137; 2,048: 124 +
+// 120 / 44 + 50; 64: 38 + 42 / 21 + 22; 8: 31 + 32 / 28 + 35; 1: 22 + 24 / 13 + 14; the copy 5 to 18.  Whole decode
+// steps of 4 layers, ms, 1 / 8 requests: 0.326 / 0.457 on the mma.sync tiles, 0.272 / 0.434 on tcgen05.
 void expert_product(const Launch& l, const Routing& r, const Tensor& a, bool gather, const Tensor& w, ExpertAct act, Tensor& out,
                     Tensor* sorted = nullptr);
 // y[t] (+)= sum_j weight[t, j] * rows[slot of (t, j)]; rows float32 [T * top, width], y float32 [T, width].
