@@ -510,6 +510,24 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
               "prefill_attention" + shape);
         return;
     }
+    // Many query heads on one key/value head (attention over a latent, few key/value heads): the heads as the rows
+    // of the tensor-core instruction, keys fetched once per sixteen heads (attention_decode_shared.cu).  Blocks of
+    // (token, group, sixteen heads) are few, so the keys are cut into enough splits for two blocks an SM, but no
+    // split shorter than four groups of 16 keys (a warp each).
+    if (s.max_q_len == 1 && q.dtype == DType::BF16 && d <= 128 && n_heads / hkv >= kSharedKvMinHeads && T <= 65535) {
+        const int max_kv = s.max_blocks * c.page_size;
+        const int tiles = hkv * ((n_heads / hkv + 15) / 16), groups = (max_kv + 15) / 16;
+        const int splits = std::max(1, std::min({(groups + 3) / 4, (2 * sm_count() + T * tiles - 1) / (T * tiles), 64}));
+        static auto need = SANDY_KERNEL(attention_decode_shared, sandy_decode_attention_shared_scratch);
+        static auto fn = SANDY_KERNEL(attention_decode_shared, sandy_decode_attention_shared);
+        const long long floats = need(T, n_heads, hkv, d, splits);
+        float* scratch = floats ? (float*)ws.raw("decode_attention_partial_rows", (size_t)floats * sizeof(float)) : nullptr;
+        OpTimer timer(l, "attention, decode (heads as rows)", attn_bytes, attn_flops);
+        check(fn(q.data, (int)q.ld, c.k, c.v, c.page_stride, s.block_table, s.max_blocks, s.token_seq, s.positions, out.data, (int)out.ld,
+                 T, n_heads, hkv, d, c.page_size, scale, window, splits, c.num_pages, sk, og, scratch, l.kernel_status, l.stream),
+              "decode_attention_shared" + shape);
+        return;
+    }
     if (s.max_q_len == 1 && decode_head_dim(q.dtype, d)) {
         const int max_kv = s.max_blocks * c.page_size;
         const int splits = std::min(decode_splits(T, n_heads, max_kv), kClusterMaxSplits);

@@ -137,6 +137,9 @@ struct AttentionExtras {
 // The widest head any attention kernel takes (the general kernel; the tensor-core prompt kernels take up to 128, the
 // decode kernels 16 / 32 / 64 / 128 and, in bfloat16, 256).
 constexpr int kMaxHeadDim = 640;
+// From this many query heads per key/value head on, a decode step's attention takes sixteen heads of a group as the
+// rows of one tensor-core product (attention_decode_shared.cu, bfloat16, heads up to 128).
+constexpr int kSharedKvMinHeads = 4;
 // Attention of a step's tokens over the cache: picks the kernel for the step's shape.
 void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const KVView& cache, Tensor& out, int n_heads,
                float scale, int window, Workspace& ws, const AttentionExtras* extras = nullptr);

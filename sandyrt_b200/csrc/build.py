@@ -44,6 +44,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "attention_decode": [],
     "attention_decode_bulk": [],
     "attention_decode_mma": [],
+    "attention_decode_shared": [],
     "attention_prefill": [],
     "attention_prefill_tc": [],
     "sampling": [],

@@ -302,6 +302,25 @@ def decode_attention(q, k_cache, v_cache, block_table, token_seq, positions, out
         LAUNCHES += 1
 
 
+def decode_attention_shared(q, k_cache, v_cache, block_table, token_seq, positions, out, *, n_heads: int, scale: float, splits: int = 1,
+                            window: int = 0, sink=None, out_gate=None) -> None:
+    """Single-token attention with the query heads of a group as the rows of one tensor-core product (bfloat16, head sizes
+    up to 128); v_cache may be k_cache itself (one plane)."""
+    _cuda(q, k_cache, v_cache, block_table, token_seq, positions, out)
+    hkv, ps, d, page_stride, num_pages = _cache_args(k_cache, v_cache)
+    T = q.shape[0]
+    lib = load_library("attention_decode_shared")
+    lib.sandy_decode_attention_shared_scratch.restype = ctypes.c_longlong
+    floats = lib.sandy_decode_attention_shared_scratch(ctypes.c_int(T), ctypes.c_int(n_heads), ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(splits))
+    scratch = torch.empty(max(int(floats), 1), dtype=torch.float32, device=q.device)
+    code = lib.sandy_decode_attention_shared(
+        _p(q), ctypes.c_int(q.stride(0)), _p(k_cache), _p(v_cache), ctypes.c_longlong(page_stride), _p(block_table),
+        ctypes.c_int(block_table.shape[1]), _p(token_seq), _p(positions), _p(out), ctypes.c_int(out.stride(0)), ctypes.c_int(T),
+        ctypes.c_int(n_heads), ctypes.c_int(hkv), ctypes.c_int(d), ctypes.c_int(ps), ctypes.c_float(scale), ctypes.c_int(window),
+        ctypes.c_int(splits), ctypes.c_int(num_pages), _p(sink), _p(out_gate), _p(scratch), _p(kernel_status(q.device)), _stream())
+    _check(code, f"decode_attention_shared(H={n_heads},Hkv={hkv},D={d})")
+
+
 def prefill_attention(q, k_cache, v_cache, block_table, q_start, kv_before, out, *, sink=None, out_gate=None, n_heads: int,
                       max_q_len: int, scale: float, window: int = 0, tc=None) -> None:
     """Tensor-core attention of prompt portions (bfloat16, head sizes 16..128 in steps of 16).

@@ -140,6 +140,14 @@ int sandy_prefill_attention_tc_ext(const void* q, int ld_q, const void* k_cache,
                                    int head_dim, int page_size, float scale, int window, int num_pages, const float* sink,
                                    const float* out_gate, int* status, cudaStream_t stream);
 
+/* attention_decode_shared.cu */
+long long sandy_decode_attention_shared_scratch(int n_tokens, int n_heads, int n_kv_heads, int head_dim, int splits);
+int sandy_decode_attention_shared(const void* q, int ld_q, const void* k_cache, const void* v_cache, long long page_stride,
+                                  const int* block_table, int max_blocks, const int* token_seq, const int* positions, void* out,
+                                  int ld_out, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size, float scale,
+                                  int window, int splits, int num_pages, const float* sink, const float* out_gate, float* scratch,
+                                  int* status, cudaStream_t stream);
+
 /* attention_prepare.cu */
 int sandy_attention_prepare(const void* proj, int ld, int q_off, int k_off, int v_off, int n_tokens, int n_heads,
                             int n_kv_heads, int qk_dim, int v_dim, int pad_dim, const float* q_gain, const float* k_gain,

@@ -119,3 +119,69 @@ def test_channel_scale_joins_one_or_two_branches():
     want = x + (g1 * y1 + g2 * y2)
     ops.scale_add(y1, g1, x, y2, g2)
     assert torch.allclose(x, want, atol=1e-6)
+
+
+# ---- single-token attention with the heads of a group as the rows of one product ----------------------------------
+def _paged(keys, values, page_size, n_kv_heads, seed):
+    """Scatter per-request keys/values [len, Hkv, D] into a poisoned paged cache with shuffled pages; one plane when
+    `values` is None.  Returns the views, the block table and the lengths."""
+    lens = [k.shape[0] for k in keys]
+    D = keys[0].shape[2]
+    blocks = [-(-n // page_size) for n in lens]
+    n_pages = sum(blocks) + 3
+    planes = 1 if values is None else 2
+    arena = torch.full((n_pages, planes, n_kv_heads, page_size, D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    order = torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    table = torch.full((len(keys), max(blocks)), -1, dtype=torch.int32)
+    for r, k in enumerate(keys):
+        for b in range(blocks[r]):
+            page = order.pop()
+            table[r, b] = page
+            n = min(page_size, lens[r] - b * page_size)
+            arena[page, 0, :, :n] = k[b * page_size:b * page_size + n].transpose(0, 1)
+            arena[page, 0, :, n:] = float("nan")
+            if values is not None:
+                arena[page, 1, :, :n] = values[r][b * page_size:b * page_size + n].transpose(0, 1)
+    k_view = arena[:, 0]
+    v_view = arena[:, 1] if values is not None else k_view
+    return k_view, v_view, table.to(DEV), lens
+
+
+@pytest.mark.parametrize("H,Hkv,D,page_size,splits,one_plane", [
+    (12, 1, 128, 16, 1, True), (12, 1, 128, 16, 5, True), (24, 1, 80, 16, 3, True), (5, 1, 16, 8, 2, True),
+    (8, 2, 64, 16, 4, False), (40, 2, 48, 32, 7, False), (16, 1, 112, 16, 64, True),
+])
+def test_decode_attention_with_heads_as_rows(H, Hkv, D, page_size, splits, one_plane):
+    g = torch.Generator().manual_seed(H * 1000 + D)
+    lens = [1, 17, 300, 64, 129]
+    keys = [torch.randn(n, Hkv, D, generator=g).to(torch.bfloat16).to(DEV) for n in lens]
+    values = None if one_plane else [torch.randn(n, Hkv, D, generator=g).to(torch.bfloat16).to(DEV) for n in lens]
+    k_view, v_view, table, _ = _paged(keys, values, page_size, Hkv, seed=D)
+    T = len(lens)
+    q = (2.0 * torch.randn(T, H * D, generator=g)).to(torch.bfloat16).to(DEV)
+    q[2] *= 3.0                                                   # sharp scores on the long request: single far keys win
+    sink = torch.randn(H, generator=g).to(DEV)
+    gate = torch.rand(T, H, generator=g).to(DEV)
+    token_seq = torch.arange(T, dtype=torch.int32, device=DEV)
+    positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    scale = D ** -0.5
+    for use_sink, use_gate in ((False, False), (True, True)):
+        out = torch.full((T, H * D), 9.0, dtype=torch.bfloat16, device=DEV)
+        ops.decode_attention_shared(q, k_view, v_view, table, token_seq, positions, out, n_heads=H, scale=scale, splits=splits,
+                                    sink=sink if use_sink else None, out_gate=gate if use_gate else None)
+        ops.check_kernel_status(out.device)
+        for t in range(T):
+            kf = keys[t].float()
+            vf = kf if one_plane else values[t].float()
+            for h in range(H):
+                kv = h // (H // Hkv)
+                s = (kf[:, kv] @ q[t, h * D:(h + 1) * D].float()) * scale
+                if use_sink:
+                    p = torch.softmax(torch.cat([s, sink[h:h + 1]]), 0)[:-1]
+                else:
+                    p = torch.softmax(s, 0)
+                want = p @ vf[:, kv]
+                if use_gate:
+                    want = want * gate[t, h]
+                got = out[t, h * D:(h + 1) * D].float()
+                assert torch.allclose(got, want, atol=3e-2, rtol=3e-2), (t, h, float((got - want).abs().max()))
