@@ -514,7 +514,11 @@ void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const K
     // of the tensor-core instruction, keys fetched once per sixteen heads (attention_decode_shared.cu).  Blocks of
     // (token, group, sixteen heads) are few, so the keys are cut into enough splits for two blocks an SM, but no
     // split shorter than four groups of 16 keys (a warp each).
-    if (s.max_q_len == 1 && q.dtype == DType::BF16 && d <= 128 && n_heads / hkv >= kSharedKvMinHeads && T <= 65535) {
+    // It is two launches with a floor of 9 us, so it takes the steps with enough (token, head, key) triples.  Alone, 12
+    // heads of 128 on one key/value head, us, this kernel / the best of the kernels below: 1 token x 392 keys 9.1 / 5.2;
+    // 8 x 392: 9.4 / 8.7; 8 tokens x 24 heads x 392: 11.3 / 16.6; 8 x 12 x 2,000: 13.2 / 36.2.
+    if (s.max_q_len == 1 && q.dtype == DType::BF16 && d <= 128 && n_heads / hkv >= kSharedKvMinHeads && T <= 65535 &&
+        (int64_t)T * n_heads * s.max_blocks * c.page_size >= kSharedKvMinTriples) {
         const int max_kv = s.max_blocks * c.page_size;
         const int tiles = hkv * ((n_heads / hkv + 15) / 16), groups = (max_kv + 15) / 16;
         const int splits = std::max(1, std::min({(groups + 3) / 4, (2 * sm_count() + T * tiles - 1) / (T * tiles), 64}));

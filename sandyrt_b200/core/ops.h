@@ -140,6 +140,7 @@ constexpr int kMaxHeadDim = 640;
 // From this many query heads per key/value head on, a decode step's attention takes sixteen heads of a group as the
 // rows of one tensor-core product (attention_decode_shared.cu, bfloat16, heads up to 128).
 constexpr int kSharedKvMinHeads = 4;
+constexpr int64_t kSharedKvMinTriples = 40000;      // tokens x heads x keys (the block table's width) from which it pays
 // Attention of a step's tokens over the cache: picks the kernel for the step's shape.
 void attention(const Launch& l, const AttentionStep& s, const Tensor& q, const KVView& cache, Tensor& out, int n_heads,
                float scale, int window, Workspace& ws, const AttentionExtras* extras = nullptr);

@@ -157,7 +157,7 @@ public:
     explicit RoutedExperts(const PartSpec& s)
         : FeedForward(s), width_(s.get_int("width")), inner_(s.get_int("inner")), E_((int)s.get_int("n_experts")),
           top_((int)s.get_int("top")), has_bias_(s.get_bool("router_bias", false)), router_(width_, E_, false, "out_in", "router") {
-        if (E_ < 1 || top_ < 1 || top_ > E_ || top_ > 32) throw ConfigError("routed_experts: top must be 1 .. min(n_experts, 32)");
+        if (E_ < 1 || E_ > 2048 || top_ < 1 || top_ > E_) throw ConfigError("routed_experts: n_experts must be 1 .. 2048 and top 1 .. n_experts");
         const std::string a = s.get_string("activation", "relu_squared");
         if (a != "relu_squared") throw ConfigError("routed_experts: unknown activation '" + a + "'");
     }

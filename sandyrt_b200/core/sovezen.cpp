@@ -218,7 +218,8 @@ void SovezenConfig::validate() const {
         if (l.mlp == "moe") {
             positive(l.ff, at + ".mlp.expert", "ff");
             positive(l.experts, at + ".mlp.router", "experts");
-            if (l.top < 1 || l.top > l.experts || l.top > 32) bad(at + ".mlp.router", "'top' must be 1 .. min(experts, 32)");
+            if (l.top < 1 || l.top > l.experts) bad(at + ".mlp.router", "'top' must be 1 .. experts");
+            if (l.experts > 2048) bad(at + ".mlp.router", "'experts' is at most 2048");
         }
         if (l.weights_of >= 0) {
             if (l.weights_of >= (int64_t)layers.size() || l.weights_of == (int64_t)i) bad(at, "'weights_of' must name another layer");

@@ -244,7 +244,9 @@ decode_shared_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __restric
     }
 }
 
-// Adds the splits' partial rows in the splits' order and finishes the rows.
+// Adds the splits' partial rows in the splits' order and finishes the rows.  One thread an element: a thread's loads of
+// the splits' values do not depend on one another, so they are in flight together (with a few elements a thread the
+// kernel was one long chain of trips to L2: 30 us for 16 splits).
 template <int D>
 __global__ void __launch_bounds__(128)
 decode_shared_merge_kernel(const float* __restrict__ scratch, int splits, bf16* __restrict__ out, int ld_out, int n_heads,
@@ -257,28 +259,30 @@ decode_shared_merge_kernel(const float* __restrict__ scratch, int splits, bf16* 
     const int first_head = kvh * group_heads + row_tile * ROWS;
     const int valid_rows = min(ROWS, group_heads - row_tile * ROWS);
     const float* base = scratch + ((size_t)t * gridDim.x + blockIdx.x) * splits * ROWS * (D + 2);
-    for (int idx = threadIdx.x; idx < valid_rows * D; idx += blockDim.x) {
-        const int row = idx / D, col = idx % D;
-        float big = -INFINITY;
-        for (int s = 0; s < splits; s++) big = fmaxf(big, base[((size_t)s * ROWS + row) * (D + 2) + D]);
-        float num = 0.0f, den = 0.0f;
-        for (int s = 0; s < splits; s++) {
-            const float* p = base + ((size_t)s * ROWS + row) * (D + 2);
-            const float f = p[D] == -INFINITY ? 0.0f : exp2f(p[D] - big);
-            num = fmaf(f, p[col], num);
-            den = fmaf(f, p[D + 1], den);
-        }
-        const int head = first_head + row;
-        if (sink) {
-            const float sk = sink[head] * LOG2E, top = fmaxf(big, sk);
-            const float f = big == -INFINITY ? 0.0f : exp2f(big - top);
-            num *= f;
-            den = den * f + exp2f(sk - top);
-        }
-        float v = den > 0.0f ? num / den : 0.0f;
-        if (out_gate) v *= out_gate[(size_t)t * n_heads + head];
-        out[(size_t)t * ld_out + (size_t)head * D + col] = __float2bfloat16_rn(v);
+    const int idx = blockIdx.z * blockDim.x + threadIdx.x;
+    const int row = idx / D, col = idx % D;
+    if (row >= valid_rows) return;
+    float big = -INFINITY;
+#pragma unroll 8
+    for (int s = 0; s < splits; s++) big = fmaxf(big, base[((size_t)s * ROWS + row) * (D + 2) + D]);
+    float num = 0.0f, den = 0.0f;
+#pragma unroll 8
+    for (int s = 0; s < splits; s++) {
+        const float* p = base + ((size_t)s * ROWS + row) * (D + 2);
+        const float f = p[D] == -INFINITY ? 0.0f : exp2f(p[D] - big);
+        num = fmaf(f, p[col], num);
+        den = fmaf(f, p[D + 1], den);
     }
+    const int head = first_head + row;
+    if (sink) {
+        const float sk = sink[head] * LOG2E, top = fmaxf(big, sk);
+        const float f = big == -INFINITY ? 0.0f : exp2f(big - top);
+        num *= f;
+        den = den * f + exp2f(sk - top);
+    }
+    float v = den > 0.0f ? num / den : 0.0f;
+    if (out_gate) v *= out_gate[(size_t)t * n_heads + head];
+    out[(size_t)t * ld_out + (size_t)head * D + col] = __float2bfloat16_rn(v);
 }
 
 template <int D>
@@ -305,7 +309,7 @@ int launch(const bf16* q, int ld_q, const bf16* k, const bf16* v, long long page
                             page_stride, block_table, max_blocks, token_seq, positions, out, ld_out, n_heads, n_kv_heads, page_size,
                             scale, window, splits, num_pages, sink, out_gate, splits > 1 ? scratch : (float*)nullptr, status);
     if (code != SANDY_OK || splits == 1) return code;
-    return sandy_launch(decode_shared_merge_kernel<D>, dim3(tiles, n_tokens), dim3(128), 0, stream, (const float*)scratch, splits, out,
+    return sandy_launch(decode_shared_merge_kernel<D>, dim3(tiles, n_tokens, (ROWS * D + 127) / 128), dim3(128), 0, stream, (const float*)scratch, splits, out,
                         ld_out, n_heads, n_kv_heads, sink, out_gate);
 }
 

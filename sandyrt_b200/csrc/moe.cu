@@ -51,7 +51,7 @@ moe_route_kernel(const float* __restrict__ logits, int ld, const float* __restri
         }
         __syncwarp();
     }
-    if (lane < top) weight_of[(size_t)t * top + lane] /= sum;      // top <= 32; lane 0's writes are visible after the syncwarp
+    for (int j = lane; j < top; j += 32) weight_of[(size_t)t * top + j] /= sum;      // lane 0's writes are visible after the syncwarp
 }
 
 __global__ void __launch_bounds__(1024)
@@ -119,12 +119,12 @@ moe_combine_kernel(const float* __restrict__ rows, int ld_rows, const float* __r
 
 }  // namespace
 
-// logits: float32 [n_tokens, >= n_experts] with pitch ld; bias float32 [n_experts] or null; 1 <= top <= min(32, n_experts).
+// logits: float32 [n_tokens, >= n_experts] with pitch ld; bias float32 [n_experts] or null; 1 <= top <= n_experts <= 2048.
 SANDY_API int sandy_moe_route(const float* logits, int ld, const float* bias, int n_tokens, int n_experts, int top,
                               int* expert_of, float* weight_of, cudaStream_t stream) {
     if (n_tokens == 0) return SANDY_OK;
     if (!logits || !expert_of || !weight_of) return SANDY_ERR_ARGUMENT;
-    if (top < 1 || top > 32 || top > n_experts || n_experts > 2048) return SANDY_ERR_UNSUPPORTED;
+    if (top < 1 || top > n_experts || n_experts > 2048) return SANDY_ERR_UNSUPPORTED;
     const int warps = 4;
     return sandy_launch(moe_route_kernel, dim3((n_tokens + warps - 1) / warps), dim3(32 * warps),
                         (size_t)warps * n_experts * sizeof(float), stream, logits, ld, bias, n_tokens, n_experts, top, expert_of,

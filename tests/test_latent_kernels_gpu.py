@@ -36,7 +36,7 @@ def test_head_product(T, G, N, K, a_gcols, o_gcols, dtype, tol):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 1.5e-2)])
-@pytest.mark.parametrize("T,E,top,width,ff", [(1, 4, 2, 32, 16), (5, 3, 3, 40, 24), (300, 16, 4, 64, 96), (130, 7, 1, 36, 20), (64, 64, 8, 128, 64)])
+@pytest.mark.parametrize("T,E,top,width,ff", [(1, 4, 2, 32, 16), (5, 3, 3, 40, 24), (300, 16, 4, 64, 96), (130, 7, 1, 36, 20), (64, 64, 8, 128, 64), (20, 48, 40, 32, 16)])
 def test_routed_experts_from_logits_to_sum(T, E, top, width, ff, dtype, tol):
     h = _rand(T, width, dtype=dtype, seed=3)
     logits = _rand(T, E, seed=4, scale=2.0)
