@@ -306,6 +306,23 @@ def test_routers_that_choose_token_by_token(tmp_path):
     _check(_run_cuts(eng, "r", ids, [33, 2, 190, 5] + [1] * 30), (cfg, w), ids, "float32", "token-by-token routing, portions")
 
 
+def test_options_at_their_edges(tmp_path):
+    """A rotated layer without a rotated part (rot_dim 0), a router that takes 40 of 48 experts, a layer without a
+    feed-forward whose file still holds its second factor (it is read past), a logit scale of one; float32."""
+    mixer = rotated(3, 16, 0, 8, 24)
+    mixer["mixer"]["rot"] = {"dims": 0, "base": 10000.0}
+    cfg = _config(67, 40, [layer(mixer, moe(48, 40, 8)), layer(plain_queries(2, 8, 8, 16, 8), None)], eps=1e-5, logit_scale=1.0)
+    w = make_weights(cfg, seed=41)
+    on_disk = dict(w)
+    on_disk["l1.ls2"] = torch.ones(40)
+    path = write_model(cfg, on_disk, str(tmp_path / "edges"))
+    ids = _tokens(cfg, 70, seed=9)
+    assert plain.router_margin(cfg, w, ids) > 1e-4
+    eng = _engine(path, "float32")
+    _check(_run_cuts(eng, "r", ids, [70]), (cfg, w), ids, "float32", "edges, whole")
+    _check(_run_cuts(eng, "r", ids, [31, 2, 30] + [1] * 7), (cfg, w), ids, "float32", "edges, in portions")
+
+
 # ---- the entry point --------------------------------------------------------------------------------------
 def test_greedy_generation_through_the_entry_point(models):
     """LLM.generate (scheduler, prompt portions, decode bursts) on three requests at once, float32: the same tokens
