@@ -91,7 +91,10 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
     extern __shared__ __align__(16) uint8_t smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
     bf16* sK = sQ + BM * LDS;                // [STAGES][BN][LDS]
-    bf16* sV = sK + STAGES * BN * LDS;       // [STAGES][BN][LDS]
+    // A cache of one plane (its values are its keys: attention over a latent) is fetched once and read twice; the
+    // block then needs half the ring, and three blocks share an SM at rows of 128 where one did.
+    const bool one_plane = k_cache == v_cache;
+    bf16* sV = one_plane ? sK : sK + STAGES * BN * LDS;       // [STAGES][BN][LDS]
     __shared__ int s_table[TABLE_SMEM];
 
     const int s = blockIdx.z, h = blockIdx.y;
@@ -146,7 +149,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ld_q, const bf16* __res
                 }
             }
             cp_async16(dk + r * LDS + c * 8, k_cache + off, ok ? 16 : 0);
-            cp_async16(dv + r * LDS + c * 8, v_cache + off, ok ? 16 : 0);
+            if (!one_plane) cp_async16(dv + r * LDS + c * 8, v_cache + off, ok ? 16 : 0);
         }
     };
     load_kv(kt_begin, 0);
@@ -337,10 +340,11 @@ int launch(const void* q, int ld_q, const void* k_cache, const void* v_cache, lo
            int n_seqs, int max_q_len, int n_heads, int n_kv_heads, int page_size, float scale, int window,
            int num_pages, const float* sink, const float* out_gate, int* status, cudaStream_t stream) {
     constexpr int LDS = D + 8;
-    const int smem = (BM + 2 * STAGES * BN) * LDS * (int)sizeof(bf16);
+    const int smem_two = (BM + 2 * STAGES * BN) * LDS * (int)sizeof(bf16);
+    const int smem = k_cache == v_cache ? (BM + STAGES * BN) * LDS * (int)sizeof(bf16) : smem_two;
     static bool configured = false;
-    if (!configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (!configured && smem_two > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_two);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
