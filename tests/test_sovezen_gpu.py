@@ -306,6 +306,40 @@ def test_routers_that_choose_token_by_token(tmp_path):
     _check(_run_cuts(eng, "r", ids, [33, 2, 190, 5] + [1] * 30), (cfg, w), ids, "float32", "token-by-token routing, portions")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_batch_decoding_with_many_heads_on_one_latent(tmp_path, dtype):
+    """Four requests of about 700 tokens decode side by side in a layer of 16 heads: 4 x 16 x 768 (token, head, key)
+    triples a step, which in bfloat16 is where the decode attention takes the heads of a group as the rows of one
+    tensor-core product (rows of 64; a second layer with rows of 128).  Scores are sharpened so that far keys win."""
+    from sandyrt_b200.engine.step import StepEntry
+
+    cfg = _config(59, 64, [layer(rotated(16, 16, 16, 8, 48, base=10000.0, scale=1.0), None),
+                           layer(plain_queries(16, 16, 8, 128, 24, scale=1.0), dense(48))], eps=1e-5, logit_scale=1.0)
+
+    def sharp(w):
+        w["l0.mix.q"] *= 3.0
+        w["l1.mix.uq"] *= 3.0
+
+    w, path = _one_model(tmp_path, cfg, seed=51, bend=sharp)
+    lengths = [700, 689, 703, 650]
+    seqs = [_tokens(cfg, n, seed=70 + i) for i, n in enumerate(lengths)]
+    eng = _engine(path, dtype, max_tokens=3072, page_size=16)
+    n_decoded = 9
+    for i, ids in enumerate(seqs):
+        eng.step([StepEntry(i, ids[:-n_decoded], [])])
+    got = [[] for _ in seqs]
+    for k in range(n_decoded):
+        out = eng.step([StepEntry(i, [ids[len(ids) - n_decoded + k]], [0]) for i, ids in enumerate(seqs)]).cpu().numpy()
+        for i in range(len(seqs)):
+            got[i].append(out[i:i + 1].copy())
+    eng.check_status()
+    for i, ids in enumerate(seqs):
+        want = _want(cfg, w, ids)[-n_decoded:]
+        bound = BOUND_F32 if dtype == "float32" else max(2e-2, 3 * rel_error(plain.forward_rounded(cfg, w, ids).numpy()[-n_decoded:], want))
+        e = rel_error(np.concatenate(got[i]), want)
+        assert e < bound, f"request {i}: relative error {e:.3e} (bound {bound:.1e})"
+
+
 def test_options_at_their_edges(tmp_path):
     """A rotated layer without a rotated part (rot_dim 0), a router that takes 40 of 48 experts, a layer without a
     feed-forward whose file still holds its second factor (it is read past), a logit scale of one; float32."""
